@@ -1,0 +1,75 @@
+"""ctypes binding of libb200moe.so (the C ABI declared in include/b200_moe.h). There is no fallback: when the library
+is missing or does not load, every entry point of the package raises."""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200moe.so")
+
+E_ARG, E_ALIGN, E_DRIVER = -1, -2, -3
+DEV_TIMEOUT = 1
+ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
+
+
+class Weights(Structure):
+    """struct b200moe_weights"""
+    _fields_ = [("w13p", c_void_p), ("sf13p", c_void_p), ("w2", c_void_p), ("sf2p", c_void_p), ("bias", c_void_p),
+                ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float)]
+
+
+_P = c_void_p
+SIGNATURES = {
+    "b200moe_version": (c_int, []),
+    "b200moe_arch": (c_char_p, []),
+    "b200moe_max_sorted_rows": (c_int64, [c_int64, c_int, c_int]),
+    "b200moe_block_rows": (c_int, [c_int64]),
+    "b200moe_preshuffle_w13": (c_int, [_P, _P, c_int, _P, _P, _P]),
+    "b200moe_preshuffle_w2_scales": (c_int, [_P, c_int, _P, _P]),
+    "b200moe_route_topk": (c_int, [_P, c_int64, c_int64, c_int, _P, c_int64, c_int, c_int, c_float, _P, _P, _P]),
+    "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
+    "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
+    "b200moe_permute": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
+    "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_gemm1_swiglu_quant": (c_int, [_P, _P, c_int, _P, _P, _P, _P, c_int64, c_int, _P, _P, _P, _P]),
+    "b200moe_gemm2_weighted": (c_int, [_P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_gemm1_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_gemm2_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P]),
+    "b200moe_reduce_slots": (c_int, [_P, _P, c_int64, _P, _P]),
+    "b200moe_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "b200moe_forward": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, c_size_t, _P, _P, _P, _P]),
+    "b200moe_forward_host": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, _P, _P, c_size_t, _P, _P, _P, _P, _P]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library with typed entry points. Raises RuntimeError when it is absent or unloadable."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m amd_kernels_b200.build` "
+                               "(nvcc, sm_100a). This package has no CPU or PyTorch fallback.")
+        try:
+            lib = ctypes.CDLL(LIB_PATH)
+        except OSError as exc:  # pragma: no cover - depends on the machine
+            raise RuntimeError(f"cannot load {LIB_PATH}: {exc}") from exc
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    """Turns a non-zero status of an entry point into an exception (ValueError for rejected arguments)."""
+    if code == 0:
+        return
+    if code in (E_ARG, E_ALIGN):
+        raise ValueError(f"{what}: rejected argument ({'alignment' if code == E_ALIGN else 'size, pointer or block height'})")
+    if code == E_DRIVER:
+        raise RuntimeError(f"{what}: the CUDA driver cannot encode tensor maps")
+    raise RuntimeError(f"{what}: CUDA error {code}")

@@ -1,0 +1,111 @@
+// Library identity, workspace carving and the whole-layer entry points.
+#include "common.cuh"
+
+namespace b200moe {
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+  float* w;               // [T][4]
+  int32_t* ids;           // [T][4]
+  uint8_t* codes;         // [T][3072]
+  uint8_t* scales;        // [T][192]
+  int32_t* sorted_ids;    // [R]
+  float* sorted_w;        // [R]
+  int32_t* block_expert;  // [R/bm]
+  int32_t* num_valid;     // [2]
+  int32_t* scratch;       // permute chunk counts
+  uint8_t* xq_sorted;     // [R][3072]
+  uint8_t* sfx;           // [R/bm][48][512]
+  uint8_t* hq;            // [R][384]
+  uint8_t* sfh;           // [R/bm][6][512]
+  size_t bytes;
+  int bm;
+  int64_t rows;
+};
+
+static Workspace carve(uint8_t* base, int64_t tokens, int num_experts) {
+  Workspace ws{};
+  ws.bm = b200moe_block_rows(tokens);
+  ws.rows = b200moe_max_sorted_rows(tokens, ws.bm, num_experts);
+  const size_t blocks = static_cast<size_t>(ws.rows / ws.bm);
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    uint8_t* p = base ? base + off : nullptr;
+    off = align_up(off + n, 1024);
+    return p;
+  };
+  ws.w = reinterpret_cast<float*>(take(tokens * kTopK * 4));
+  ws.ids = reinterpret_cast<int32_t*>(take(tokens * kTopK * 4));
+  ws.codes = take(tokens * (kH / 2));
+  ws.scales = take(tokens * (kH / 32));
+  ws.sorted_ids = reinterpret_cast<int32_t*>(take(ws.rows * 4));
+  ws.sorted_w = reinterpret_cast<float*>(take(ws.rows * 4));
+  ws.block_expert = reinterpret_cast<int32_t*>(take(blocks * 4));
+  ws.num_valid = reinterpret_cast<int32_t*>(take(16));
+  ws.scratch = reinterpret_cast<int32_t*>(take(b200moe_permute_scratch_bytes(tokens, num_experts) + 16));
+  ws.xq_sorted = take(ws.rows * (kH / 2));
+  ws.sfx = take(blocks * (kH / 128) * kAtomBytes);
+  ws.hq = take(ws.rows * (kI / 2));
+  ws.sfh = take(blocks * (kI / 128) * kAtomBytes);
+  ws.bytes = off;
+  return ws;
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_version(void) { return 1; }
+extern "C" const char* b200moe_arch(void) { return "sm_100a"; }
+
+extern "C" size_t b200moe_workspace_bytes(int64_t tokens, int num_experts) {
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 1 || num_experts > b200moe::kMaxE) return 0;
+  return b200moe::carve(nullptr, tokens, num_experts).bytes;
+}
+
+extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, const float* logits, int64_t tokens,
+                               void* workspace, size_t workspace_bytes, void* slots_bf16, void* out_bf16,
+                               int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w || !x_bf16 || !logits || !workspace || !slots_bf16 || !status) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS) return B200MOE_E_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200MOE_E_ALIGN;
+  const int ne = w->num_experts;
+  Workspace ws = carve(static_cast<uint8_t*>(workspace), tokens, ne);
+  if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
+  int r;
+  if ((r = b200moe_route_topk(logits, ne, 0, 1, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.w, ws.ids, stream)))
+    return r;
+  if ((r = b200moe_quant_mxfp4(x_bf16, tokens, kH, ws.codes, ws.scales, stream))) return r;
+  if ((r = b200moe_permute(ws.ids, ws.w, tokens, ne, ws.bm, ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid,
+                           ws.scratch, stream)))
+    return r;
+  if ((r = b200moe_dispatch_rows(ws.codes, ws.scales, ws.sorted_ids, ws.num_valid, tokens, ws.bm, ws.rows, ws.xq_sorted,
+                                 ws.sfx, stream)))
+    return r;
+  if ((r = b200moe_gemm1_swiglu_quant(w->w13p, w->sf13p, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows,
+                                      ws.bm, ws.hq, ws.sfh, status, stream)))
+    return r;
+  if ((r = b200moe_gemm2_weighted(w->w2, w->sf2p, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids,
+                                  ws.sorted_w, ws.rows, ws.bm, tokens, slots_bf16, status, stream)))
+    return r;
+  if (out_bf16 && (r = b200moe_reduce_slots(slots_bf16, nullptr, tokens, out_bf16, stream))) return r;
+  return 0;
+}
+
+extern "C" int b200moe_forward_host(const b200moe_weights* w, const void* host_x_bf16, const float* host_logits,
+                                    int64_t tokens, void* dev_x, float* dev_logits, void* workspace,
+                                    size_t workspace_bytes, void* slots_bf16, void* dev_out, void* host_out_bf16,
+                                    int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w || !host_x_bf16 || !host_logits || !dev_x || !dev_logits || !dev_out || !host_out_bf16) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS) return B200MOE_E_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(dev_x, host_x_bf16, tokens * kH * 2, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpyAsync(dev_logits, host_logits, tokens * w->num_experts * 4, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int r = b200moe_forward(w, dev_x, dev_logits, tokens, workspace, workspace_bytes, slots_bf16, dev_out, status, stream);
+  if (r) return r;
+  e = cudaMemcpyAsync(host_out_bf16, dev_out, tokens * kH * 2, cudaMemcpyDeviceToHost, s);
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}

@@ -1,0 +1,65 @@
+// Shared constants and device helpers of libb200moe (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200_moe.h"
+
+namespace b200moe {
+
+constexpr int kH = B200MOE_H;        // hidden size
+constexpr int kI = B200MOE_I;        // intermediate size (per expert, after SwiGLU)
+constexpr int kTopK = B200MOE_TOPK;
+constexpr int kMaxE = B200MOE_E;
+
+constexpr int kW13Tiles = 2 * kI / 128;  // 12 tiles of 64 gate + 64 up rows per expert
+constexpr int kW2Tiles = kH / 128;       // 48
+constexpr int kK1Tiles = kH / 256;       // 24 K-tiles (256 elements = 128 bytes) in GEMM1
+constexpr int kK2Tiles = kI / 256;       // 3 in GEMM2
+constexpr int kAtomBytes = 512;          // one scale atom
+
+#define B200MOE_CHECK_LAUNCH()                        \
+  do {                                                \
+    cudaError_t e__ = cudaGetLastError();             \
+    if (e__ != cudaSuccess) return static_cast<int>(e__); \
+  } while (0)
+
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+  // {0,.5,1,1.5,2,3,4,6} with the sign in bit 3
+  const uint32_t m = code & 7u;
+  float v = (m < 2u) ? 0.5f * static_cast<float>(m)
+                     : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+  return (code & 8u) ? -v : v;
+}
+
+__device__ __forceinline__ float e8m0_value(uint32_t byte) {
+  // 2^(byte-127); byte 0 is 2^-127 (a subnormal float)
+  return byte ? __uint_as_float(byte << 23) : __uint_as_float(0x00400000u);
+}
+
+// "Quark even" block scale from the block's absolute maximum: max(1, (bits(amax) - 0x00E00000) >> 23), arithmetic shift.
+__device__ __forceinline__ int quark_even_e8m0(float amax) {
+  int e = (static_cast<int>(__float_as_uint(amax)) - 0x00E00000) >> 23;
+  return e < 1 ? 1 : e;
+}
+
+// E2M1 code of v at scale byte e: number of midpoints below |v| / 2^(e-127), ties to the even code, sign from the bit.
+__device__ __forceinline__ uint32_t e2m1_code(float v, int e) {
+  const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);  // 2^(127-e), e <= 253
+  const float a = fabsf(v) * inv;
+  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
+  return c | ((__float_as_uint(v) >> 31) << 3);
+}
+
+__device__ __forceinline__ float swiglu_oai(float g, float u) {
+  g = fminf(g, 7.0f);
+  u = fminf(fmaxf(u, -7.0f), 7.0f);
+  const float sig = 1.0f / (1.0f + __expf(-1.702f * g));
+  return g * sig * (u + 1.0f);
+}
+
+// byte offset of scale j (0..3) of row r (0..127) inside a 512-byte scale atom
+__device__ __host__ __forceinline__ int atom_offset(int r, int j) { return (r & 31) * 16 + (r >> 5) * 4 + j; }
+
+}  // namespace b200moe

@@ -1,0 +1,477 @@
+// Grouped MXFP4 x MXFP4 GEMMs on the sm_100a tensor cores (tcgen05.mma kind::mxf4, block scale per 32, fp32
+// accumulators in tensor memory), one persistent CTA per SM.
+//
+// Orientation: the weight tile is the 128-row M operand, the expert's token block (16/32/64/128 sorted rows) is the N
+// operand. So one pass over an expert's weights serves its whole block, the accumulator of output feature i sits in TMEM
+// lane i, and a token is a TMEM column.
+//
+//   warp 0    producer: one thread issues TMA tile loads (128B-swizzled FP4 tiles) and bulk copies of scale atoms
+//   warp 1    MMA: allocates TMEM; one thread copies scale atoms to TMEM (tcgen05.cp) and issues tcgen05.mma
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator, then
+//             GEMM1: SwiGLU-OAI (gate and up rows of one tile live in neighbouring lane quarters), MXFP4 requantisation
+//                    of 32 intermediate columns = the 32 lanes of a warp, codes and scale atoms to global memory
+//             GEMM2: times the routing weight, bf16, one store per (token, slot, column)
+//
+// Every mbarrier wait is bounded: after about two seconds it records B200MOE_DEV_TIMEOUT in the status word, raises a
+// CTA-wide abort flag, the roles drain and the CTA frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicExch(status, B200MOE_DEV_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// AND of a predicate over the 128 epilogue threads (named barrier 1); every one of them gets the result.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, 1, 128, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return out != 0;
+}
+
+// K-major operand tile in shared memory, 128-byte rows, 128B swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// One 512-byte scale atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+}
+
+// ------------------------------------------------------------------------------------------------ kernel
+template <int MODE, int BM>
+struct Cfg {
+  static constexpr int kTilesM = MODE == 1 ? kW13Tiles : kW2Tiles;
+  static constexpr int kTilesK = MODE == 1 ? kK1Tiles : kK2Tiles;
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = BM * 128;
+  static constexpr int kSfBytes = 2 * kAtomBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
+  static constexpr int kStages = BM == 128 ? 6 : (BM == 64 ? 7 : 8);
+  static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
+  static constexpr int kSfaCol = 2 * kAccCols;
+  static constexpr int kSfbCol = kSfaCol + 8;
+  static constexpr int kColsUsed = kSfbCol + 8;
+  static constexpr int kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the first tile to 1024 bytes
+  static constexpr int kActAtomsPerBlock = MODE == 1 ? kH / 128 : kI / 128;  // activation scale atoms per row block
+};
+
+struct EpilogueArgs {
+  // GEMM1
+  uint8_t* hq;
+  uint8_t* sfh;
+  // GEMM2
+  const int32_t* sorted_ids;
+  const float* sorted_w;
+  __nv_bfloat16* slots;
+  int64_t tokens;
+};
+
+constexpr int kThreads = 192;
+
+template <int MODE, int BM>
+__global__ void __launch_bounds__(kThreads, 1)
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        const uint8_t* __restrict__ sf_w, const uint8_t* __restrict__ sf_x,
+                        const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid,
+                        EpilogueArgs ep, int32_t* status) {
+  using C = Cfg<MODE, BM>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[C::kStages];
+  __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ float exch[MODE == 1 ? 2 : 1][2][16][32];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abort_v = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_tfull[a]), 1);
+      mbar_init(smem_u32(&bar_tempty[a]), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int n_blocks = num_valid[0] / BM;
+  const int total_units = n_blocks * C::kTilesM;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const int b = u / C::kTilesM, mt = u % C::kTilesM;
+        const int e = block_expert[b];
+        const int w_row = (e * C::kTilesM + mt) * 128;
+        const uint8_t* sfa_src = sf_w + static_cast<int64_t>(e * C::kTilesM + mt) * C::kTilesK * C::kSfBytes;
+        const uint8_t* sfb_src = sf_x + static_cast<int64_t>(b) * C::kActAtomsPerBlock * kAtomBytes;
+        for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t base = tiles + s * C::kStageBytes;
+          mbar_arrive_expect_tx(full, C::kStageBytes);
+          tma_load_2d(base, &map_w, kt * 128, w_row, full);
+          tma_load_2d(base + C::kABytes, &map_x, kt * 128, b * BM, full);
+          bulk_load(base + C::kABytes + C::kBBytes, sfa_src + kt * C::kSfBytes, C::kSfBytes, full);
+          bulk_load(base + C::kABytes + C::kBBytes + C::kSfBytes, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
+        }
+      }
+      if (!ok) {
+        // aborting: let the copies already in flight land before the CTA gives up its shared memory
+        const uint32_t pending = it < C::kStages ? it : C::kStages;
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t idx = it - 1 - j, s = idx % C::kStages, ph = (idx / C::kStages) & 1u;
+          const uint64_t t0 = global_timer();
+          while (!mbar_try_wait(smem_u32(&bar_full[s]), ph) && global_timer() - t0 < kWaitLimitNs) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BM >> 3) << 17) | (1u << 23) | (8u << 24);
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+        const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
+        for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t base = tiles + s * C::kStageBytes;
+          const uint32_t sfa = base + C::kABytes + C::kBBytes, sfb = sfa + C::kSfBytes;
+          tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(sfa));
+          tc_cp_scales(tmem_base + C::kSfaCol + 4, scale_desc(sfa + kAtomBytes));
+          tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(sfb));
+          tc_cp_scales(tmem_base + C::kSfbCol + 4, scale_desc(sfb + kAtomBytes));
+          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 64 elements = 32 bytes per MMA; scales: atom k/2, bytes {0,1} or {2,3} of each row's 4-byte cell
+            const uint32_t sf_id = (k & 1) * 2u;
+            const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
+            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
+                        tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
+          }
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5, TMEM lane quarter = warp % 4)
+    const int q = warp & 3;
+    uint32_t ui = 0, chunk_no = 0;
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
+      const int b = u / C::kTilesM, mt = u % C::kTilesM;
+      const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+      // the four warps must agree before they meet at the named barrier below
+      if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status))) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
+      const int64_t row0 = static_cast<int64_t>(b) * BM;
+#pragma unroll 1
+      for (int c = 0; c < BM / 16; ++c, ++chunk_no) {
+        uint32_t v[16];
+        tc_ld16(t_acc + c * 16, v);
+        if (MODE == 1) {
+          float(*ex)[32] = exch[chunk_no & 1][q >> 1];
+          if (q & 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ex[j][lane] = __uint_as_float(v[j]);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (!(q & 1)) {
+            const int g = 2 * mt + (q >> 1);  // 32-column group of the intermediate, 0..23
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = c * 16 + j;
+              const float h = swiglu_oai(__uint_as_float(v[j]), ex[j][lane]);
+              const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h))));
+              const int sc = quark_even_e8m0(amax);
+              uint32_t code = e2m1_code(h, sc);
+              code |= __shfl_down_sync(0xffffffffu, code, 1) << 4;
+              code |= __shfl_down_sync(0xffffffffu, code, 2) << 8;
+              code |= __shfl_down_sync(0xffffffffu, code, 4) << 16;
+              if ((lane & 7) == 0)
+                *reinterpret_cast<uint32_t*>(ep.hq + (row0 + n) * (kI / 2) + g * 16 + (lane >> 3) * 4) = code;
+              if (lane == 0)
+                ep.sfh[(static_cast<int64_t>(b) * (kI / 128) + (g >> 2)) * kAtomBytes + atom_offset(n, g & 3)] =
+                    static_cast<uint8_t>(sc);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t row = row0 + c * 16 + j;
+            const int sid = __ldg(ep.sorted_ids + row);
+            const int64_t token = sid & 0x00ffffff;
+            if (token < ep.tokens) {
+              const float wt = __ldg(ep.sorted_w + row);
+              ep.slots[(token * kTopK + (sid >> 24)) * kH + mt * 128 + q * 32 + lane] =
+                  __float2bfloat16_rn(__uint_as_float(v[j]) * wt);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_tempty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// byte matrix [rows][row_bytes], boxes of 128 bytes x box_rows, 128B swizzle
+static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200MOE_E_DRIVER;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
+}
+
+static int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <int MODE, int BM>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const uint8_t* sf_w, const uint8_t* sf_x,
+                  const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
+                  int32_t* status, cudaStream_t stream) {
+  using C = Cfg<MODE, BM>;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               C::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int64_t max_units = max_rows / BM * C::kTilesM;
+  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  if (grid <= 0) return 0;
+  grouped_gemm_kernel<MODE, BM><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep,
+                                                                          status);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}
+
+template <int MODE>
+static int launch_bm(int bm, const CUtensorMap& mw, const CUtensorMap& mx, const uint8_t* sf_w, const uint8_t* sf_x,
+                     const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
+                     int32_t* status, cudaStream_t stream) {
+  switch (bm) {
+    case 16: return launch<MODE, 16>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 32: return launch<MODE, 32>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 64: return launch<MODE, 64>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 128: return launch<MODE, 128>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+  }
+  return B200MOE_E_ARG;
+}
+
+static bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
+
+}  // namespace b200moe
+
+extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13p, const uint8_t* sf13p, int num_experts,
+                                          const uint8_t* xq_sorted, const uint8_t* sfx, const int32_t* block_expert,
+                                          const int32_t* num_valid, int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh,
+                                          int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w13p || !sf13p || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status)
+    return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || (bm != 16 && bm != 32 && bm != 64 && bm != 128) ||
+      max_rows % bm)
+    return B200MOE_E_ARG;
+  if (misaligned(w13p, 16) || misaligned(sf13p, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) ||
+      misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  CUtensorMap mw, mx;
+  int r = make_map(&mw, w13p, kH / 2, static_cast<uint64_t>(num_experts) * 2 * kI, 128);
+  if (r) return r;
+  r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  if (r) return r;
+  EpilogueArgs ep{};
+  ep.hq = hq;
+  ep.sfh = sfh;
+  return launch_bm<1>(bm, mw, mx, sf13p, sfx, block_expert, num_valid, ep, max_rows, status,
+                      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_gemm2_weighted(const uint8_t* w2, const uint8_t* sf2p, int num_experts, const uint8_t* hq,
+                                      const uint8_t* sfh, const int32_t* block_expert, const int32_t* num_valid,
+                                      const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm,
+                                      int64_t tokens, void* slots_bf16, int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w2 || !sf2p || !hq || !sfh || !block_expert || !num_valid || !sorted_ids || !sorted_w || !slots_bf16 || !status)
+    return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || tokens < 0 ||
+      (bm != 16 && bm != 32 && bm != 64 && bm != 128) || max_rows % bm)
+    return B200MOE_E_ARG;
+  if (misaligned(w2, 16) || misaligned(sf2p, 16) || misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  CUtensorMap mw, mx;
+  int r = make_map(&mw, w2, kI / 2, static_cast<uint64_t>(num_experts) * kH, 128);
+  if (r) return r;
+  r = make_map(&mx, hq, kI / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  if (r) return r;
+  EpilogueArgs ep{};
+  ep.sorted_ids = sorted_ids;
+  ep.sorted_w = sorted_w;
+  ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
+  ep.tokens = tokens;
+  return launch_bm<2>(bm, mw, mx, sf2p, sfh, block_expert, num_valid, ep, max_rows, status,
+                      static_cast<cudaStream_t>(stream));
+}
+

@@ -1,0 +1,93 @@
+// bf16 -> MXFP4 activation quantisation (row-major) and the gather of quantised rows into sorted order.
+#include "common.cuh"
+
+namespace b200moe {
+
+// One thread = 8 consecutive bf16 (16 bytes in, 4 bytes out); 4 neighbouring threads share one 32-element block.
+__global__ void __launch_bounds__(256) quant_mxfp4_kernel(const uint4* __restrict__ x, int64_t n_vec, int k,
+                                                          uint32_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool live = i < n_vec;  // n_vec is a multiple of 32 per row, so a 4-thread group is live or dead together
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = x[i];
+  float v[8];
+  const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(r[j] << 16);
+    v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const int e = quark_even_e8m0(amax);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) packed |= e2m1_code(v[j], e) << (4 * j);
+  if (live) {
+    codes[i] = packed;
+    if ((threadIdx.x & 3) == 0) scales[i >> 2] = static_cast<uint8_t>(e);
+  }
+  (void)k;
+}
+
+// One warp per sorted row: copies the token's 3072 code bytes and scatters its 192 scale bytes into the block's atoms.
+__global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __restrict__ codes,
+                                                            const uint8_t* __restrict__ scales,
+                                                            const int32_t* __restrict__ sorted_ids,
+                                                            const int32_t* __restrict__ num_valid, int64_t tokens,
+                                                            int bm, uint8_t* __restrict__ xq_sorted,
+                                                            uint8_t* __restrict__ sfx) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= num_valid[0]) return;
+  const int64_t token = sorted_ids[row] & 0x00ffffff;
+  const bool pad = token >= tokens;
+  uint4* dst = reinterpret_cast<uint4*>(xq_sorted + row * (kH / 2));
+  const uint4* src = reinterpret_cast<const uint4*>(codes + token * (kH / 2));
+#pragma unroll
+  for (int j = 0; j < (kH / 2) / 16 / 32; ++j)
+    dst[j * 32 + lane] = pad ? make_uint4(0, 0, 0, 0) : src[j * 32 + lane];
+  const int64_t block = row / bm;
+  const int r = static_cast<int>(row % bm);
+  const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(scales + token * (kH / 32));
+  uint8_t* sdst = sfx + block * (kH / 128) * kAtomBytes + atom_offset(r, 0);
+  for (int a = lane; a < kH / 128; a += 32)
+    *reinterpret_cast<uint32_t*>(sdst + a * kAtomBytes) = pad ? 0x7f7f7f7fu : ssrc[a];
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, uint8_t* codes, uint8_t* scales,
+                                   void* stream) {
+  using namespace b200moe;
+  if (!x_bf16 || !codes || !scales || tokens < 0 || k <= 0 || (k % 256) != 0) return B200MOE_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(codes) & 3)) return B200MOE_E_ALIGN;
+  if (tokens == 0) return 0;
+  const int64_t n_vec = tokens * (k / 8);
+  const unsigned grid = static_cast<unsigned>((n_vec + 255) / 256);
+  quant_mxfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x_bf16), n_vec, k, reinterpret_cast<uint32_t*>(codes), scales);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
+                                     const int32_t* num_valid, int64_t tokens, int bm, int64_t max_rows,
+                                     uint8_t* xq_sorted, uint8_t* sfx, void* stream) {
+  using namespace b200moe;
+  if (!codes || !scales || !sorted_ids || !num_valid || !xq_sorted || !sfx || tokens < 0 || max_rows < 0)
+    return B200MOE_E_ARG;
+  if (bm != 16 && bm != 32 && bm != 64 && bm != 128) return B200MOE_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(xq_sorted) & 15) ||
+      (reinterpret_cast<uintptr_t>(scales) & 3) || (reinterpret_cast<uintptr_t>(sfx) & 15))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
+  dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, scales, sorted_ids, num_valid,
+                                                                            tokens, bm, xq_sorted, sfx);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}

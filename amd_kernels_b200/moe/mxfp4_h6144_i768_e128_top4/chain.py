@@ -1,0 +1,350 @@
+"""Routed MXFP4 H6144 I768 E128 top4 on B200: the host side of the entry, mirroring the reference's
+``amd_kernels/moe/mxfp4_h6144_i768_e128_top4/chain.py`` (names, argument meaning and error behaviour), on top of the
+C ABI of libb200moe.so. PyTorch is used for device memory and streams only; every computation is a kernel of the library.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+
+import torch
+
+from ... import _lib
+
+H, I, E, TOPK = 6144, 768, 128, 4  # noqa: E741
+MAX_TOKENS = 87381  # reference chain.py:13-18: variant_for raises above
+ROUTING_MODES = {"sigmoid_bias": _lib.ROUTE_SIGMOID_BIAS, "softmax": _lib.ROUTE_SOFTMAX}
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_status: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 word kernels write device-side conditions to (0 = none, 1 = a bounded wait ran out)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status[key]
+
+
+def last_status(device=None) -> int:
+    """Synchronises and returns the device status word (and clears it)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = status_word(dev)
+    value = int(word.item())
+    word.zero_()
+    return value
+
+
+def variant_for(n_tokens: int) -> int:
+    """The block height (sorted rows per expert block) served at ``n_tokens``; ValueError outside 1..87381, the range
+    the reference's ``variant_for`` accepts (chain.py:53-57)."""
+    if not 0 < n_tokens <= MAX_TOKENS:
+        raise ValueError(f"unsupported token count {n_tokens}")
+    return int(_lib.load().b200moe_block_rows(n_tokens))
+
+
+@dataclass
+class MoeWeights:
+    """The router (fp32 [E, H]) and bias (fp32 [E]), and the experts in the kernels' layouts, built once by
+    ``from_row_major`` before graph capture (reference chain.py:23-50).
+
+    ``w13`` [E, 12, 128, 3072] u8: tiles of 64 gate + 64 up rows in 32-row groups; ``w13_scale`` [E, 12, 24, 2, 512]
+    scale atoms; ``w2`` [E, 6144, 384] u8 in checkpoint order; ``w2_scale`` [E, 48, 3, 2, 512] scale atoms."""
+    router_weight: torch.Tensor | None
+    correction_bias: torch.Tensor | None
+    w13: torch.Tensor
+    w13_scale: torch.Tensor
+    w2: torch.Tensor
+    w2_scale: torch.Tensor
+    routed_scaling_factor: float = 2.0
+    routing_mode: str = "sigmoid_bias"
+    shared_weights: object | None = None
+    row_major: tuple | None = None  # the checkpoint tensors, kept only on request (the CUDA-core cross-check reads them)
+    _abi: object = field(default=None, repr=False)
+
+    @classmethod
+    def from_row_major(cls, router_weight, correction_bias, w13, w13_scale, w2, w2_scale, *, shared=None,
+                       routed_scaling_factor=2.0, routing_mode="sigmoid_bias", keep_row_major=False):
+        """Checkpoint layout (row-major uint8 MXFP4 codes / e8m0 scales, gate rows then up rows) -> the kernels'
+        layouts. ``routing_mode``: "sigmoid_bias" (the reference's rule) or "softmax" (top-4 of the softmax,
+        renormalised). ``shared`` (the MXFP8 shared expert) is accepted and must be None in this build."""
+        reason = unsupported_reason(w13, w13_scale, w2, w2_scale, None, None, None, None, routed_only=True)
+        if reason is not None:
+            raise ValueError(reason)
+        if shared is not None:
+            raise ValueError("the MXFP8 shared expert is not built: pass shared=None")
+        if routing_mode not in ROUTING_MODES:
+            raise ValueError(f"routing_mode must be one of {sorted(ROUTING_MODES)}")
+        if not w13.is_cuda:
+            raise ValueError("weights must be CUDA tensors")
+        lib = _lib.load()
+        n_exp = w13.shape[0]
+        dev = w13.device
+        w13, w13_scale, w2, w2_scale = (t.contiguous() for t in (w13, w13_scale, w2, w2_scale))
+        w13p = torch.empty((n_exp, 12, 128, H // 2), dtype=torch.uint8, device=dev)
+        sf13 = torch.empty((n_exp, 12, 24, 2, 512), dtype=torch.uint8, device=dev)
+        sf2 = torch.empty((n_exp, 48, 3, 2, 512), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.b200moe_preshuffle_w13(_ptr(w13), _ptr(w13_scale), n_exp, _ptr(w13p), _ptr(sf13),
+                                                  _stream(dev)), "preshuffle_w13")
+            _lib.check(lib.b200moe_preshuffle_w2_scales(_ptr(w2_scale), n_exp, _ptr(sf2), _stream(dev)),
+                       "preshuffle_w2_scales")
+        bias = None if correction_bias is None else correction_bias.to(device=dev, dtype=torch.float32).contiguous()
+        return cls(router_weight, bias, w13p, sf13, w2, sf2, float(routed_scaling_factor), routing_mode,
+                   shared_weights=None, row_major=(w13, w13_scale, w2, w2_scale) if keep_row_major else None)
+
+    @property
+    def num_experts(self) -> int:
+        return self.w13.shape[0]
+
+    def abi(self) -> _lib.Weights:
+        """``struct b200moe_weights`` over this object's tensors."""
+        if self._abi is None:
+            self._abi = _lib.Weights(self.w13.data_ptr(), self.w13_scale.data_ptr(), self.w2.data_ptr(),
+                                     self.w2_scale.data_ptr(),
+                                     None if self.correction_bias is None else self.correction_bias.data_ptr(),
+                                     self.num_experts, ROUTING_MODES[self.routing_mode],
+                                     self.routed_scaling_factor)
+        return self._abi
+
+
+def unsupported_reason(w13, w13_scale, w2, w2_scale, shared_w13, shared_s13, shared_w2, shared_s2,
+                       swiglu=(1.702, 7.0, 1.0), *, routed_only=False) -> str | None:
+    """None when ``MoeWeights.from_row_major`` takes these checkpoint-layout tensors, else the reason
+    (reference __init__.py:19-35). ``routed_only`` skips the shared-expert tensors, which this build does not use."""
+    ref = (1.702, 7.0, 1.0)
+    if any(abs(a - b) > 1e-6 for a, b in zip(swiglu, ref)):
+        return f"needs SwiGLU-OAI (alpha, limit, beta) {ref}, got {tuple(swiglu)}"
+    n_exp = w13.shape[0] if w13 is not None and w13.ndim == 3 and routed_only else E
+    spec = [("w13", w13, (n_exp, 2 * I, H // 2), torch.uint8), ("w13_scale", w13_scale, (n_exp, 2 * I, H // 32), torch.uint8),
+            ("w2", w2, (n_exp, H, I // 2), torch.uint8), ("w2_scale", w2_scale, (n_exp, H, I // 32), torch.uint8)]
+    if not routed_only:
+        spec += [("shared w13", shared_w13, (2 * I, H), torch.float8_e4m3fn), ("shared w13 scale", shared_s13, (2 * I, H // 32), None),
+                 ("shared w2", shared_w2, (H, I), torch.float8_e4m3fn), ("shared w2 scale", shared_s2, (H, I // 32), None)]
+    for name, t, shape, dtype in spec:
+        if t is None or tuple(t.shape) != shape or (dtype is not None and t.dtype != dtype):
+            got = None if t is None else (tuple(t.shape), t.dtype)
+            return f"{name}: needs {shape} {dtype or 'e8m0'}, got {got}"
+    if not 1 <= n_exp <= E:
+        return f"w13: needs 1..{E} experts, got {n_exp}"
+    return None
+
+
+# ------------------------------------------------------------------------------------------------ single kernels
+def mxfp4_quant(x: torch.Tensor):
+    """bf16 [M, K] -> (codes u8 [M, K/2], e8m0 u8 [M, K/32]) row-major (reference quant.py:32 ``mxfp4_quant``)."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[1] % 256:
+        raise ValueError("expected contiguous BF16 [M, K] with K a multiple of 256")
+    m, k = x.shape
+    codes = torch.empty((m, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((m, k // 32), dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.load().b200moe_quant_mxfp4(_ptr(x), m, k, _ptr(codes), _ptr(scales), _stream(x.device)), "quant_mxfp4")
+    return codes, scales
+
+
+def topk_route(logits: torch.Tensor, bias, scale: float, mode: str = "sigmoid_bias"):
+    """fp32 logits [M, E] or split-K partials [M, S, E] (any strides on M and S) -> (weights fp32 [M, 4], ids int32
+    [M, 4]) (reference router_topk.py:239 ``splitk_biased_topk``)."""
+    if logits.dtype != torch.float32 or logits.ndim not in (2, 3) or logits.stride(-1) != 1:
+        raise ValueError("expected fp32 [M, E] logits or [M, S, E] partials, unit stride on E")
+    m, n_exp = logits.shape[0], logits.shape[-1]
+    splits, stride_s = (1, 0) if logits.ndim == 2 else (logits.shape[1], logits.stride(1))
+    wt = torch.empty((m, TOPK), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((m, TOPK), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.load().b200moe_route_topk(_ptr(logits), logits.stride(0), stride_s, splits, _ptr(bias), m, n_exp,
+                                              ROUTING_MODES[mode], scale, _ptr(wt), _ptr(ids), _stream(logits.device)),
+               "route_topk")
+    return wt, ids
+
+
+@dataclass
+class SortBuffers:
+    """The routing sort's outputs (reference common/sort.py:19-65)."""
+    sorted_ids: torch.Tensor
+    sorted_weights: torch.Tensor
+    block_expert: torch.Tensor
+    num_valid: torch.Tensor
+    bm: int
+    tokens: int
+
+    @property
+    def max_rows(self) -> int:
+        return self.sorted_ids.shape[0]
+
+
+def moe_sort(topk_ids: torch.Tensor, topk_weights: torch.Tensor, bm: int, num_experts: int = E) -> SortBuffers:
+    """ids int32 [M, 4], weights fp32 [M, 4] -> expert-sorted, block-padded rows in pair order."""
+    if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32 or topk_ids.shape != topk_weights.shape \
+            or topk_ids.ndim != 2 or topk_ids.shape[1] != TOPK:
+        raise ValueError("expected int32 ids and fp32 weights of shape [M, 4]")
+    lib = _lib.load()
+    m, dev = topk_ids.shape[0], topk_ids.device
+    variant_for(m)
+    rows = int(lib.b200moe_max_sorted_rows(m, bm, num_experts))
+    buf = SortBuffers(torch.empty(rows, dtype=torch.int32, device=dev), torch.empty(rows, dtype=torch.float32, device=dev),
+                      torch.empty(rows // bm, dtype=torch.int32, device=dev), torch.empty(2, dtype=torch.int32, device=dev),
+                      bm, m)
+    scratch_bytes = int(lib.b200moe_permute_scratch_bytes(m, num_experts))
+    scratch = torch.empty(max(scratch_bytes // 4, 1), dtype=torch.int32, device=dev)
+    _lib.check(lib.b200moe_permute(_ptr(topk_ids.contiguous()), _ptr(topk_weights.contiguous()), m, num_experts, bm,
+                                   _ptr(buf.sorted_ids), _ptr(buf.sorted_weights), _ptr(buf.block_expert),
+                                   _ptr(buf.num_valid), _ptr(scratch), _stream(dev)), "permute")
+    return buf
+
+
+def dispatch_rows(x_quant, sort: SortBuffers):
+    """Row-major (codes, scales) -> (codes in sorted-row order [rows, 3072], scale atoms [rows/bm, 48, 512])."""
+    codes, scales = x_quant
+    dev = codes.device
+    xq = torch.empty((sort.max_rows, H // 2), dtype=torch.uint8, device=dev)
+    sfx = torch.empty((sort.max_rows // sort.bm, H // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().b200moe_dispatch_rows(_ptr(codes), _ptr(scales), _ptr(sort.sorted_ids), _ptr(sort.num_valid),
+                                                 sort.tokens, sort.bm, sort.max_rows, _ptr(xq), _ptr(sfx), _stream(dev)),
+               "dispatch_rows")
+    return xq, sfx
+
+
+def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
+    """GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 -> (h codes [rows, 384], h scale atoms [rows/bm, 6, 512])."""
+    dev = xq_sorted.device
+    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant(_ptr(w.w13), _ptr(w.w13_scale), w.num_experts, _ptr(xq_sorted),
+                                                      _ptr(sfx), _ptr(sort.block_expert), _ptr(sort.num_valid),
+                                                      sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
+                                                      _ptr(status_word(dev)), _stream(dev)), "gemm1_swiglu_quant")
+    return hq, sfh
+
+
+def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):
+    """GEMM2 x routing weight -> bf16 slots [M, 4, 6144] (rows of padded or absent pairs are left untouched)."""
+    dev = hq.device
+    if slots is None:
+        slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.load().b200moe_gemm2_weighted(_ptr(w.w2), _ptr(w.w2_scale), w.num_experts, _ptr(hq), _ptr(sfh),
+                                                  _ptr(sort.block_expert), _ptr(sort.num_valid), _ptr(sort.sorted_ids),
+                                                  _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens,
+                                                  _ptr(slots), _ptr(status_word(dev)), _stream(dev)), "gemm2_weighted")
+    return slots
+
+
+def simt_gemm1(x_quant, sort: SortBuffers, w: MoeWeights, rows=None):
+    """The CUDA-core cross-check of ``grouped_gemm1`` on the checkpoint-layout weights (``keep_row_major=True``)."""
+    if w.row_major is None:
+        raise ValueError("needs MoeWeights.from_row_major(..., keep_row_major=True)")
+    codes, scales = x_quant
+    dev = codes.device
+    hq = torch.zeros((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.zeros((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().b200moe_gemm1_simt(_ptr(w.row_major[0]), _ptr(w.row_major[1]), _ptr(codes), _ptr(scales),
+                                              _ptr(sort.sorted_ids), _ptr(sort.block_expert), _ptr(sort.num_valid),
+                                              _ptr(rows), 0 if rows is None else rows.numel(), sort.max_rows, sort.bm,
+                                              sort.tokens, _ptr(hq), _ptr(sfh), _stream(dev)), "gemm1_simt")
+    return hq, sfh
+
+
+def simt_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, rows=None, slots=None):
+    """The CUDA-core cross-check of ``grouped_gemm2``."""
+    if w.row_major is None:
+        raise ValueError("needs MoeWeights.from_row_major(..., keep_row_major=True)")
+    dev = hq.device
+    if slots is None:
+        slots = torch.zeros((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.load().b200moe_gemm2_simt(_ptr(w.row_major[2]), _ptr(w.row_major[3]), _ptr(hq), _ptr(sfh),
+                                              _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), _ptr(sort.block_expert),
+                                              _ptr(sort.num_valid), _ptr(rows), 0 if rows is None else rows.numel(),
+                                              sort.max_rows, sort.bm, sort.tokens, _ptr(slots), _stream(dev)), "gemm2_simt")
+    return slots
+
+
+def reduce_slots(slots: torch.Tensor, shared: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [M, 4, H] (+ bf16 [M, H]) -> bf16 [M, H], slots 0..3 then shared in fp32, one rounding
+    (reference common/reduce_slots_shared.py:37-41)."""
+    if slots.dtype != torch.bfloat16 or slots.ndim != 3 or slots.shape[1:] != (TOPK, H) or not slots.is_contiguous():
+        raise ValueError("expected contiguous BF16 [M, 4, 6144]")
+    out = torch.empty((slots.shape[0], H), dtype=torch.bfloat16, device=slots.device)
+    _lib.check(_lib.load().b200moe_reduce_slots(_ptr(slots), _ptr(shared), slots.shape[0], _ptr(out),
+                                                _stream(slots.device)), "reduce_slots")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ the entry
+def _logits(x, w, router_logits):
+    if router_logits is not None:
+        if router_logits.shape != (x.shape[0], w.num_experts) or router_logits.dtype != torch.float32:
+            raise ValueError(f"router_logits: expected fp32 [{x.shape[0]}, {w.num_experts}]")
+        return router_logits.contiguous()
+    if w.router_weight is None:
+        raise ValueError("needs router_logits= or MoeWeights with router_weight")
+    # plain library GEMM in fp32 (the bf16x3 split-K router kernel of the reference is not rebuilt)
+    return torch.matmul(x.float(), w.router_weight.float().t()).contiguous()
+
+
+def route(x, w, router_logits=None):
+    """The entry's routing (topk weights incl. the routed scale, topk ids), exposed for numerical checks
+    (reference chain.py:106-110)."""
+    logits = _logits(x, w, router_logits)
+    return topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
+
+
+def mxfp4_moe_experts(x_quant, topk_weights, topk_ids, w):
+    """The routed experts on the MXFP4 input ``x_quant`` = (codes, scales), already routed (``topk_weights`` include
+    the routed scale) -> the BF16 [M, 4, H] slots (reference chain.py:113-124). Served at every M here."""
+    n = x_quant[0].shape[0]
+    bm = variant_for(n)
+    sort = moe_sort(topk_ids, topk_weights, bm, w.num_experts)
+    xq, sfx = dispatch_rows(x_quant, sort)
+    hq, sfh = grouped_gemm1(xq, sfx, sort, w)
+    return grouped_gemm2(hq, sfh, sort, w)
+
+
+def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
+    """Normed BF16 [M, 6144] -> the routed experts' output (reference chain.py:127-197).
+
+    Reduced mode returns BF16 [M, 6144] = slots 0..3 summed in fp32; partials mode returns (slots BF16 [M, 4, H], None)
+    (the second item is the shared expert's output in the reference). ``router_logits`` fp32 [M, E] skips the router
+    GEMM. One call = one ``b200moe_forward`` on the current stream; scratch and outputs come from ``torch.empty``."""
+    if not isinstance(x, torch.Tensor):
+        raise ValueError("prepared inputs (MoeInput / MoeInputCompact) are not built")
+    variant_for(x.shape[0])
+    if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expected contiguous BF16 [M,6144]")
+    lib = _lib.load()
+    n, dev = x.shape[0], x.device
+    logits = _logits(x, w, router_logits)
+    ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    slots = torch.empty((n, TOPK, H), dtype=torch.bfloat16, device=dev)
+    out = None if return_partials else torch.empty((n, H), dtype=torch.bfloat16, device=dev)
+    _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
+                                   _ptr(slots), _ptr(out), _ptr(status_word(dev)), _stream(dev)), "forward")
+    return (slots, None) if return_partials else out
+
+
+WARM_UP_TOKENS = (1, 16, 129, 513, 1025)  # one size per block height (16, 16, 32, 64, 128)
+
+
+def warm_up_mxfp4_moe(w, *, partials=False, workers=None):
+    """Loads the library and runs one call per kernel variant before serving, so that the first served call (or a CUDA
+    graph capture) does no one-time set-up (reference chain.py:239-258; there is nothing to compile here, ``workers``
+    is accepted and ignored)."""
+    dev = w.w13.device
+    with torch.inference_mode():
+        for m in WARM_UP_TOKENS:
+            x = torch.zeros((m, H), device=dev, dtype=torch.bfloat16)
+            lg = torch.zeros((m, w.num_experts), device=dev, dtype=torch.float32)
+            mxfp4_moe(x, w, return_partials=False, router_logits=lg)
+            if partials:
+                mxfp4_moe(x, w, return_partials=True, router_logits=lg)
+    torch.cuda.synchronize(dev)
+    if last_status(dev):
+        raise RuntimeError("a kernel reported a device-side timeout during warm-up")

@@ -1,0 +1,152 @@
+/*
+ * C ABI of libb200moe.so: the routed MXFP4 x MXFP4 MoE block (hidden 6144, intermediate 768, up to 128 experts, top-4)
+ * as hand-written sm_100a kernels. Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (passed as void*, a cudaStream_t), launches on that stream without synchronising, allocates nothing unless stated, and
+ * returns an int status: 0 = launched, negative = rejected argument (B200MOE_E_*), positive = CUDA runtime error code.
+ * Device-side conditions (a bounded wait that ran out) are reported through the caller-provided `status` word, which a
+ * kernel sets to a non-zero B200MOE_DEV_* code and never clears; callers zero it before a call and read it after a sync.
+ *
+ * Each function names the reference interface it replaces, as path:line inside the amd-kernels project with
+ * MOE/ = amd_kernels/moe/mxfp4_h6144_i768_e128_top4/.
+ *
+ * Data formats
+ *   E2M1 codes: two per byte along K, even element in the low nibble; code = index into {0,.5,1,1.5,2,3,4,6} | sign<<3.
+ *   E8M0 scales: one byte per 32 elements along K, value 2^(byte-127).
+ *   "scale atom": 512 bytes holding 4 consecutive scale bytes of up to 128 rows, byte (r%32)*16 + (r/32)*4 + j for row r
+ *   and scale j -- the image tcgen05.cp.32x128b.warpx4 moves to tensor memory in one instruction.
+ *   Preshuffled W13 [E][12][128][3072]: tile t, row r holds gate (r/32 even) or up (r/32 odd) row
+ *   64*t + 32*(r/64) + r%32 of the checkpoint (gate rows 0..767, up rows 768..1535). W2 keeps the checkpoint order.
+ *   Weight scales: [E][tiles][K/256][2 atoms], activations scales: [row block][K/128 atoms].
+ *   Sorted rows: (token, slot) pairs grouped by expert ascending, pair order 4*token+slot inside an expert, every expert
+ *   padded to a multiple of bm rows; sorted_ids = token | slot<<24, padding rows carry token = T and weight 0.
+ */
+#ifndef B200_MOE_H
+#define B200_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_H 6144
+#define B200MOE_I 768
+#define B200MOE_E 128
+#define B200MOE_TOPK 4
+#define B200MOE_MAX_TOKENS 87381 /* MOE/chain.py:13-18, variant_for rejects more */
+
+#define B200MOE_E_ARG (-1)     /* null pointer, size out of range, unsupported bm */
+#define B200MOE_E_ALIGN (-2)   /* a pointer that must be 16-byte (workspace: 256-byte) aligned is not */
+#define B200MOE_E_DRIVER (-3)  /* the CUDA driver entry point for tensor maps is unavailable */
+#define B200MOE_DEV_TIMEOUT 1  /* a bounded mbarrier wait ran out inside a kernel */
+
+#define B200MOE_ROUTE_SIGMOID_BIAS 0 /* the reference's rule */
+#define B200MOE_ROUTE_SOFTMAX 1      /* softmax, top-4, renormalised over the picks */
+
+/* Library version and the SM architecture it was built for ("sm_100a"). */
+int b200moe_version(void);
+const char* b200moe_arch(void);
+
+/* Upper bound of padded sorted rows for T tokens and block height bm (MOE/common/sort.py:19-23, max_sorted_rows). */
+int64_t b200moe_max_sorted_rows(int64_t tokens, int bm, int num_experts);
+
+/* Block height the library picks for T tokens: 16 / 32 / 64 / 128 (role of MOE/chain.py:13-18 DISPATCH, by size only). */
+int b200moe_block_rows(int64_t tokens);
+
+/* Weight preshuffle, once at load time (MOE/chain.py:41-50 MoeWeights.from_row_major; MOE/layout.py:24-38 w13_layout,
+ * w2_layout; MOE/prefill_h6144_i768.py:34-45 Mxfp4PrefillScales.from_row_major). Checkpoint tensors in, kernel layouts
+ * out (see "Data formats"); all device pointers; w2 codes need no permutation and are used in place. */
+int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_scale, int num_experts, uint8_t* w13p,
+                           uint8_t* sf13p, void* stream);
+int b200moe_preshuffle_w2_scales(const uint8_t* w2_scale, int num_experts, uint8_t* sf2p, void* stream);
+
+/* Router top-4 (MOE/router_topk.py:239-272 splitk_biased_topk). logits[t][e] = sum over s<S of
+ * partials[t*stride_t + s*stride_s + e], added from 0.0 in split order; plain logits are S=1. mode SIGMOID_BIAS:
+ * s = sigmoid(logit), choice = s + bias[e], weight = s*scale / sum of the 4 chosen s. mode SOFTMAX: choice = logit,
+ * weight = scale * exp(l - max) / sum over the 4 picks. Picks are in descending choice order, exactly equal choices go
+ * to the lower expert id. bias may be null (zero). out_w fp32 [T][4], out_ids int32 [T][4]. */
+int b200moe_route_topk(const float* partials, int64_t stride_t, int64_t stride_s, int splits, const float* bias,
+                       int64_t tokens, int num_experts, int mode, float scale, float* out_w, int32_t* out_ids,
+                       void* stream);
+
+/* Activation quantisation bf16 [T][K] -> codes [T][K/2], scales [T][K/32], row-major, bit-exact "Quark even" rule
+ * (MOE/quant.py:32-106 mxfp4_quant; oracle MOE/reference.py:32-46). K is a multiple of 256. */
+int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, uint8_t* codes, uint8_t* scales, void* stream);
+
+/* Routing sort (MOE/common/sort.py:19-65 SortBuffers; MOE/sort_a16w4.py:217-242 moe_sort_a16w4;
+ * MOE/common/sort_count_all.py:188 moe_sort_count_all). ids/w [T][4] -> sorted_ids int32 [max_rows], sorted_w fp32
+ * [max_rows], block_expert int32 [max_rows/bm], num_valid int32 [2] = {padded rows, first row of the last non-empty
+ * expert}. `scratch` is int32 [ceil(4T/1024)][num_experts], needed only when 4T > 1024 (b200moe_permute_scratch_bytes). */
+size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
+int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
+                    float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
+
+/* Gather of quantised token rows into sorted order with the scales laid out as atoms (the activation-scale gather of
+ * MOE/common/scale_sort_tile_map.py:253 scale_sort_tile_map, plus the row gather the reference does inside GEMM1,
+ * MOE/gemm1_prefill_h6144_i768.py:209-228). xq_sorted [max_rows][3072], sfx [max_rows/bm][48][512]; padding rows are
+ * written as zero codes with scale byte 127. */
+int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
+                          const int32_t* num_valid, int64_t tokens, int bm, int64_t max_rows, uint8_t* xq_sorted,
+                          uint8_t* sfx, void* stream);
+
+/* Grouped GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 block-scaled FP4 MMA
+ * (MOE/gemm1_prefill_h6144_i768.py:71-898, MOE/gemm1_a4w4_small.py:75-164; oracle MOE/reference.py:66-72).
+ * hq [max_rows][384] codes of h in sorted-row order, sfh [max_rows/bm][6][512] scale atoms. All pointers 16-byte
+ * aligned. `status` (device int32) receives B200MOE_DEV_* codes. */
+int b200moe_gemm1_swiglu_quant(const uint8_t* w13p, const uint8_t* sf13p, int num_experts, const uint8_t* xq_sorted,
+                               const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
+                               int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream);
+
+/* Grouped GEMM2, times the routing weight, rounded to bf16, one writer per (token, slot, column)
+ * (MOE/gemm2_a4w4_small.py:19-79, MOE/gemm2_a4w4_bm128.py:52; oracle MOE/reference.py:73-74).
+ * slots bf16 [T][4][6144]; padding rows are dropped. */
+int b200moe_gemm2_weighted(const uint8_t* w2, const uint8_t* sf2p, int num_experts, const uint8_t* hq,
+                           const uint8_t* sfh, const int32_t* block_expert, const int32_t* num_valid,
+                           const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm, int64_t tokens,
+                           void* slots_bf16, int32_t* status, void* stream);
+
+/* Plain CUDA-core versions of the two grouped GEMMs on checkpoint-layout weights and row-major activations, same
+ * outputs and output layouts as the tcgen05 kernels. They exist so the tensor-core kernels and the preshuffle can be
+ * checked on the GPU at sizes the CPU oracle cannot reach; the product path never selects them. `rows`/`n_rows`: the
+ * sorted rows to compute (null = all rows below num_valid[0]). */
+int b200moe_gemm1_simt(const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* codes, const uint8_t* scales,
+                       const int32_t* sorted_ids, const int32_t* block_expert, const int32_t* num_valid,
+                       const int32_t* rows, int64_t n_rows, int64_t max_rows, int bm, int64_t tokens, uint8_t* hq,
+                       uint8_t* sfh, void* stream);
+int b200moe_gemm2_simt(const uint8_t* w2, const uint8_t* w2_scale, const uint8_t* hq, const uint8_t* sfh,
+                       const int32_t* sorted_ids, const float* sorted_w, const int32_t* block_expert,
+                       const int32_t* num_valid, const int32_t* rows, int64_t n_rows, int64_t max_rows, int bm,
+                       int64_t tokens, void* slots_bf16, void* stream);
+
+/* Slot reduce (MOE/common/reduce_slots_shared.py:16-41 reduce_slots_shared; oracle MOE/reference.py:151-159):
+ * out = bf16( (((+0 + s0) + s1) + s2) + s3 (+ shared) ) in fp32, bit-exact. shared may be null. */
+int b200moe_reduce_slots(const void* slots_bf16, const void* shared_bf16, int64_t tokens, void* out_bf16, void* stream);
+
+/* The whole routed layer on one stream (MOE/chain.py:127-197 mxfp4_moe without the shared expert): route -> quantise
+ * -> sort -> gather -> GEMM1 -> GEMM2 -> (reduce). `workspace` of b200moe_workspace_bytes(T, num_experts) bytes,
+ * 256-byte aligned; out bf16 [T][6144] may be null when only slots [T][4][6144] are wanted (partials mode). */
+typedef struct b200moe_weights {
+  const uint8_t* w13p;
+  const uint8_t* sf13p;
+  const uint8_t* w2;
+  const uint8_t* sf2p;
+  const float* bias; /* may be null */
+  int num_experts;
+  int route_mode;
+  float route_scale;
+} b200moe_weights;
+size_t b200moe_workspace_bytes(int64_t tokens, int num_experts);
+int b200moe_forward(const b200moe_weights* w, const void* x_bf16, const float* logits, int64_t tokens, void* workspace,
+                    size_t workspace_bytes, void* slots_bf16, void* out_bf16, int32_t* status, void* stream);
+
+/* Host-buffer form of the same call, the one the end-to-end benchmark times: copies x and logits from (pinned) host
+ * memory to `dev_x`/`dev_logits`, runs b200moe_forward, copies out to `host_out`, all on `stream`, no synchronise. */
+int b200moe_forward_host(const b200moe_weights* w, const void* host_x_bf16, const float* host_logits, int64_t tokens,
+                         void* dev_x, float* dev_logits, void* workspace, size_t workspace_bytes, void* slots_bf16,
+                         void* dev_out, void* host_out_bf16, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MOE_H */
