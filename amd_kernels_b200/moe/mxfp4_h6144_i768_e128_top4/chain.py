@@ -31,7 +31,8 @@ def status_word(device) -> torch.Tensor:
     """The per-device int32 word kernels write device-side conditions to (0 = none, 1 = a bounded wait ran out)."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        with torch.inference_mode(False):  # a normal tensor even when first used under inference_mode
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
     return _status[key]
 
 

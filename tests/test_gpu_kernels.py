@@ -1,0 +1,167 @@
+"""GPU parity tests of the single kernels, called through the C ABI, against the CPU oracle and the golden fixtures.
+Bit-exact: quantisation codes and scales, routing ids, the permutation, the slot reduce. Routing weights: relative 2^-20
+(the reference's WEIGHT_RTOL, reference.py:114-115)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from tests.conftest import golden
+from tests.util import atoms_to_rowmajor, bf16_dev, bits_of, dev, make_routing
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import chain
+    return chain
+
+
+def replay_check(fn):
+    """Run eagerly, capture in a CUDA graph, poison the captured outputs (NaN / 0xA5), replay; returns (eager, replayed)
+    — the reference's fixture (tests/moe/.../workload.py:134-149)."""
+    eager = [t.clone() for t in fn()]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = fn()
+    for t in captured:
+        if t.dtype.is_floating_point and t.element_size() > 1:
+            t.fill_(float("nan"))
+        else:
+            t.view(torch.uint8).fill_(0xA5)
+    graph.replay()
+    torch.cuda.synchronize()
+    return eager, captured
+
+
+def test_quant_golden_fixture(C):
+    g = golden("quant.npz")
+    q, s = C.mxfp4_quant(bf16_dev(g["x_bits"]))
+    assert np.array_equal(s.cpu().numpy(), g["scales"])
+    assert np.array_equal(q.cpu().numpy(), g["codes"])
+
+
+@pytest.mark.parametrize("m", [1, 300, 4097])
+def test_quant_binades_zero_blocks_midpoints(C, m):
+    # recipe of the reference's tests/moe/.../test_quant.py:25-31
+    gen = torch.Generator().manual_seed(m)
+    x = torch.randn((m, 192, 32), generator=gen)
+    x *= torch.exp2(torch.randint(-20, 21, (m, 192, 1), generator=gen).float())
+    x[torch.rand((m, 192), generator=gen) < 0.02] = 0.0
+    x = x.view(m, 6144).bfloat16()
+    rq, rs = orc.quant_mxfp4(x.float().numpy())
+    xd = x.cuda()
+    q, s = C.mxfp4_quant(xd)
+    assert np.array_equal(s.cpu().numpy(), rs) and np.array_equal(q.cpu().numpy(), rq)
+    for _ in range(2):
+        q2, s2 = C.mxfp4_quant(xd)
+        assert torch.equal(q, q2) and torch.equal(s, s2)
+    eager, replayed = replay_check(lambda: list(C.mxfp4_quant(xd)))
+    assert all(torch.equal(a, b) for a, b in zip(eager, replayed))
+
+
+def test_quant_rejects_bad_input(C):
+    with pytest.raises(ValueError):
+        C.mxfp4_quant(torch.zeros((4, 6144), device="cuda"))
+    with pytest.raises(ValueError):
+        C.mxfp4_quant(torch.zeros((4, 100), device="cuda", dtype=torch.bfloat16))
+
+
+def test_route_golden_partials(C):
+    # split-K partials summed in split order, the reference's rule, exact ties included (routing.npz)
+    g = golden("routing.npz")
+    parts = dev(g["partials"].transpose(1, 0, 2).copy()).permute(1, 0, 2)  # [M,S,E] view of [S,M,E], as the routers write
+    wt, ids = C.topk_route(parts, dev(g["bias"]), 2.0, "sigmoid_bias")
+    dec = g["decided"]
+    assert np.array_equal(ids.cpu().numpy()[dec], g["ids"][dec])
+    rows = dec.all(1)
+    np.testing.assert_allclose(wt.cpu().numpy()[rows], g["weights"][rows], rtol=orc.WEIGHT_RTOL)
+    # exact ties go to the lower expert id: an all-equal row picks 0,1,2,3 when the bias is flat
+    wt0, ids0 = C.topk_route(parts, None, 2.0, "sigmoid_bias")
+    assert ids0[0].tolist() == [0, 1, 2, 3]
+    np.testing.assert_allclose(wt0[0].cpu().numpy(), 0.5, rtol=1e-6)
+
+
+@pytest.mark.parametrize("m", [1, 2, 17, 256, 2049, 8192])
+@pytest.mark.parametrize("mode", ["softmax", "sigmoid_bias"])
+def test_route_matches_oracle(C, m, mode):
+    rng = np.random.default_rng(m)
+    lg = rng.standard_normal((m, 128)).astype(np.float32)
+    if m > 2:
+        lg[1] = 0.25          # a whole row of ties
+        lg[2, 3:40] = 5.0     # a block of ties on top
+    bias = (rng.standard_normal(128) * 0.1).astype(np.float32)
+    bias[::7] = 0.0
+    scale = 1.0 if mode == "softmax" else 2.0
+    wt, ids = C.topk_route(dev(lg), dev(bias), scale, mode)
+    if mode == "softmax":
+        wr, ir, vals = orc.route_softmax(lg, scale)
+        dec = np.ones(ir.shape, bool)  # exact compares on fp32 logits: every id is pinned, ties included
+    else:
+        wr, ir, vals = orc.route_sigmoid_bias(lg, bias, scale)
+        dec = orc.decided(vals)
+    assert np.array_equal(ids.cpu().numpy()[dec], ir[dec])
+    rows = dec.all(1)
+    np.testing.assert_allclose(wt.cpu().numpy()[rows], wr[rows], rtol=orc.WEIGHT_RTOL)
+    wt2, ids2 = C.topk_route(dev(lg), dev(bias), scale, mode)
+    assert torch.equal(ids, ids2) and torch.equal(wt, wt2)
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 64, 255, 256, 257, 1000, 4097])
+@pytest.mark.parametrize("kind", ["uniform", "hot", "four", "one", "dup"])
+def test_permute_bit_exact(C, m, kind):
+    ids, w = make_routing(m, kind, seed=31 + m)
+    for bm in (16, 32, 64, 128):
+        sb = C.moe_sort(dev(ids), dev(w), bm)
+        rows, wts, blocks, nv = orc.permute(ids, w, bm)
+        assert np.array_equal(sb.num_valid.cpu().numpy(), nv)
+        assert np.array_equal(sb.sorted_ids.cpu().numpy()[:nv[0]], rows)
+        assert np.array_equal(sb.sorted_weights.cpu().numpy()[:nv[0]].view(np.uint32), wts.view(np.uint32))
+        assert np.array_equal(sb.block_expert.cpu().numpy()[:nv[0] // bm], blocks)
+
+
+def test_permute_largest_size_and_replay(C):
+    m = 87381
+    ids, w = make_routing(m, "uniform", seed=1)
+    ids_d, w_d = dev(ids), dev(w)
+    sb = C.moe_sort(ids_d, w_d, 128)
+    rows, wts, blocks, nv = orc.permute(ids, w, 128)
+    assert np.array_equal(sb.num_valid.cpu().numpy(), nv)
+    assert np.array_equal(sb.sorted_ids.cpu().numpy()[:nv[0]], rows)
+    assert np.array_equal(sb.block_expert.cpu().numpy()[:nv[0] // 128], blocks)
+    eager, replayed = replay_check(lambda: [(s := C.moe_sort(ids_d, w_d, 128)).sorted_ids, s.sorted_weights, s.num_valid])
+    n = int(eager[2][0])
+    assert torch.equal(eager[2], replayed[2]) and torch.equal(eager[0][:n], replayed[0][:n])
+    assert torch.equal(eager[1][:n], replayed[1][:n])
+
+
+@pytest.mark.parametrize("m,bm", [(3, 16), (40, 32), (100, 64), (300, 128)])
+def test_dispatch_rows_gathers_codes_and_scale_atoms(C, m, bm):
+    rng = np.random.default_rng(m)
+    codes = rng.integers(0, 256, (m, 3072), dtype=np.uint8)
+    scales = rng.integers(100, 140, (m, 192), dtype=np.uint8)
+    ids, w = make_routing(m, "hot", seed=m)
+    sb = C.moe_sort(dev(ids), dev(w), bm)
+    xq, sfx = C.dispatch_rows((dev(codes), dev(scales)), sb)
+    nv = int(sb.num_valid[0])
+    rows = sb.sorted_ids.cpu().numpy()[:nv]
+    tok = rows & 0xFFFFFF
+    live = tok < m
+    got = xq.cpu().numpy()[:nv]
+    assert np.array_equal(got[live], codes[tok[live]]) and not got[~live].any()
+    sc = atoms_to_rowmajor(sfx.cpu().numpy(), bm)[:nv]
+    assert np.array_equal(sc[live], scales[tok[live]]) and np.all(sc[~live] == 127)
+
+
+def test_reduce_golden_and_shared(C):
+    g = golden("reduce.npz")
+    slots = bf16_dev(g["slots"])
+    out = C.reduce_slots(slots)
+    assert np.array_equal(bits_of(out), g["out"])
+    shared = torch.randn((8, 6144), device="cuda").bfloat16()
+    out = C.reduce_slots(slots, shared)
+    assert np.array_equal(bits_of(out), orc.reduce_slots_bf16(g["slots"], bits_of(shared)))
+    with pytest.raises(ValueError):
+        C.reduce_slots(slots.float())

@@ -1,0 +1,260 @@
+"""GPU parity tests of the grouped GEMMs and the whole entry, through the C ABI.
+
+Tolerances (the reference's, its tests/moe/.../test_entry.py:45-58,131-141 and reference.py:78-83): slot sums against
+the fp32 oracle on the same MXFP4 operands: cosine >= 0.9999 over the output, relative L2 < 4e-3, and max-abs error
+below MAX_ABS (stated here: 2% of the output's largest magnitude). Bit-exact: routing ids, the permutation, h codes and
+scales against the CUDA-core cross-check, repeated calls, CUDA-graph replays, and one token's slots whatever the batch.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from tests.conftest import golden
+from tests.util import (H, atoms_to_rowmajor, bf16_dev, bits_of, cosine, dev, make_routing, oracle_slots, rel_l2)
+
+pytestmark = pytest.mark.gpu
+COS_MIN, REL_L2_MAX, MAX_ABS_FRACTION = 0.9999, 4e-3, 0.02
+
+
+@pytest.fixture(scope="module")
+def C():
+    from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import chain
+    return chain
+
+
+@pytest.fixture(scope="module")
+def layer(C, config0):
+    """Configuration 0's weights on the GPU in both layouts, softmax routing (scale 1)."""
+    raw, xb, lg = config0
+    w = C.MoeWeights.from_row_major(None, None, *(dev(a) for a in raw), routing_mode="softmax",
+                                    routed_scaling_factor=1.0, keep_row_major=True)
+    return raw, w, xb, lg
+
+
+def check_against_oracle(got, ref):
+    assert np.isfinite(got).all()
+    assert cosine(got, ref) >= COS_MIN, cosine(got, ref)
+    assert rel_l2(got, ref) < REL_L2_MAX, rel_l2(got, ref)
+    assert np.abs(got - ref).max() <= MAX_ABS_FRACTION * np.abs(ref).max(), np.abs(got - ref).max()
+
+
+def run_stages(C, w, xq, ids, wts, bm, tc=True, rows=None):
+    sb = C.moe_sort(ids, wts, bm, w.num_experts)
+    if tc:
+        hq, sfh = C.grouped_gemm1(*C.dispatch_rows(xq, sb), sb, w)
+        slots = C.grouped_gemm2(hq, sfh, sb, w, slots=torch.zeros((sb.tokens, 4, H), dtype=torch.bfloat16, device="cuda"))
+    else:
+        hq, sfh = C.simt_gemm1(xq, sb, w, rows)
+        slots = C.simt_gemm2(hq, sfh, sb, w, rows)
+    return sb, hq, sfh, slots
+
+
+@pytest.mark.parametrize("tokens,bm", [(1, 16), (16, 16), (40, 32), (100, 64), (200, 128), (300, 16)])
+@pytest.mark.parametrize("kind", ["uniform", "one", "dup"])
+def test_tensor_core_gemms_equal_cuda_core_gemms(C, tokens, bm, kind):
+    """4 experts, every block height: h codes and scales and the bf16 slots equal the CUDA-core kernels bit for bit
+    (both accumulate exact products in fp32; codes could differ only at rounding ties, which these seeds do not hit)."""
+    (w13, s13, w2, s2), gen = orc.make_weights(seed=tokens, experts=4)
+    xb, _ = orc.make_inputs(gen, tokens, experts=4)
+    w = C.MoeWeights.from_row_major(None, None, dev(w13), dev(s13), dev(w2), dev(s2), keep_row_major=True)
+    ids, wts = make_routing(tokens, kind, seed=tokens, experts=4)
+    xq = C.mxfp4_quant(bf16_dev(xb))
+    sb, hq, sfh, slots = run_stages(C, w, xq, dev(ids), dev(wts), bm)
+    _, hq_r, sfh_r, slots_r = run_stages(C, w, xq, dev(ids), dev(wts), bm, tc=False)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    nv = int(sb.num_valid[0])
+    live = ((sb.sorted_ids[:nv] & 0xFFFFFF) < tokens).cpu().numpy()
+    a, b = hq[:nv].cpu().numpy()[live], hq_r[:nv].cpu().numpy()[live]
+    assert (a != b).mean() < 1e-4
+    sa, sr = (atoms_to_rowmajor(t.cpu().numpy(), bm)[:nv][live] for t in (sfh, sfh_r))
+    assert (sa != sr).mean() < 1e-4
+    if np.array_equal(a, b):
+        assert torch.equal(slots, slots_r)
+    check_against_oracle(slots.float().cpu().numpy().sum(1), slots_r.float().cpu().numpy().sum(1))
+
+
+def test_config0_against_reference_golden(C, layer):
+    """Configuration 0 (T=16) end to end against the output of the reference's own w4a4_moe_ref."""
+    raw, w, xb, lg = layer
+    g = golden("moe_config0.npz")
+    x, logits = bf16_dev(xb), dev(lg)
+    wt, ids = C.route(x, w, router_logits=logits)
+    assert np.array_equal(ids.cpu().numpy(), g["ids_softmax"])
+    np.testing.assert_allclose(wt.cpu().numpy(), g["weights_softmax"], rtol=orc.WEIGHT_RTOL)
+    q, s = C.mxfp4_quant(x)
+    assert np.array_equal(q.cpu().numpy(), g["xq"]) and np.array_equal(s.cpu().numpy(), g["xs"])
+    out = C.mxfp4_moe(x, w, router_logits=logits)
+    slots, shared = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0 and shared is None
+    check_against_oracle(out.float().cpu().numpy(), g["out_softmax"])
+    check_against_oracle(slots.float().sum(1).cpu().numpy(), g["out_softmax"])
+    assert np.array_equal(bits_of(out), orc.reduce_slots_bf16(bits_of(slots)))
+    for _ in range(3):
+        assert torch.equal(out, C.mxfp4_moe(x, w, router_logits=logits))
+
+
+def test_reference_routing_rule_and_distributions(C):
+    """The reference's own test distributions: scale bytes 118..123, activations 0.5*N(0,1), sigmoid + bias routing
+    with the routed scale 2 (tests/moe/.../workload.py:34-35,88-90; test_entry.py:18-25)."""
+    (w13, s13, w2, s2), gen = orc.make_weights(seed=9, scale_lo=118, scale_hi=124)
+    tokens = 12
+    x = (torch.randn((tokens, H), generator=gen) * 0.5).bfloat16()
+    gate = torch.randn((128, H), generator=gen) / H ** 0.5
+    bias = torch.randn((128,), generator=gen) * 0.01
+    w = C.MoeWeights.from_row_major(gate.cuda(), bias.cuda(), dev(w13), dev(s13), dev(w2), dev(s2))
+    xd = x.cuda()
+    wt, ids = C.route(xd, w)
+    logits = (x.double() @ gate.double().t())
+    wr, ir, vals = orc.route_sigmoid_bias(logits.numpy(), bias.numpy(), 2.0)
+    dec = orc.decided(vals, eps=1e-4)  # logits come from an fp32 library GEMM here, not from the fp64 product
+    assert np.array_equal(ids.cpu().numpy()[dec], ir[dec]) and dec.mean() > 0.95
+    np.testing.assert_allclose(wt.cpu().numpy()[dec.all(1)], wr[dec.all(1)], atol=1e-3, rtol=0)
+    out = C.mxfp4_moe(xd, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    xq, xs = orc.quant_mxfp4(x.float().numpy())
+    ref = orc.w4a4_moe(xq, xs, w13, s13, w2, s2, wt.cpu().numpy(), ids.cpu().numpy())
+    check_against_oracle(out.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 4, 8, 16, 32, 64, 128, 256])
+def test_decode_sweep_with_graph_padding_rows(C, layer, tokens):
+    """The decode sizes; the last quarter of the rows are CUDA-graph padding (zero rows, ordinary logits). Checked
+    against the CUDA-core kernels on every row, against the CPU oracle on four tokens, replayed from a CUDA graph."""
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(1000 + tokens)
+    xb, lg = orc.make_inputs(gen, tokens, pad_rows=tokens // 4)
+    x, logits = bf16_dev(xb), dev(lg)
+    out = C.mxfp4_moe(x, w, router_logits=logits)
+    slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+    wt, ids = C.route(x, w, router_logits=logits)
+    xq = C.mxfp4_quant(x)
+    _, _, _, slots_r = run_stages(C, w, xq, ids, wt, C.variant_for(tokens), tc=False)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    got, ref = slots.float().cpu().numpy(), slots_r.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    if tokens // 4:
+        assert not got[tokens - tokens // 4:].any() and not bits_of(out)[tokens - tokens // 4:].any()
+    assert cosine(got, ref) >= 0.99999 and rel_l2(got, ref) < 2e-3
+    pick = np.unique(np.linspace(0, tokens - 1, 4).astype(int))
+    cpu = oracle_slots(xq[0].cpu().numpy(), xq[1].cpu().numpy(), raw, ids.cpu().numpy(), wt.cpu().numpy(), pick)
+    if np.abs(cpu).max() > 0:
+        check_against_oracle(got[pick].sum(1), cpu.sum(1))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = C.mxfp4_moe(x, w, router_logits=logits)
+    captured.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, out) and C.last_status() == 0
+
+
+@pytest.mark.parametrize("tokens,kind", [(2048, "softmax"), (8192, "softmax"), (4096, "zipf")])
+def test_full_size_properties(C, layer, tokens, kind):
+    """Prefill sizes, where the CPU oracle is out of reach: (1) sampled sorted rows equal the CUDA-core kernels,
+    (2) sixteen tokens agree with the CPU oracle, (3) a token's slots are bit-identical whether it runs in this batch or
+    in a batch of 16 (each token is its own accumulator column), (4) two runs are bit-identical, (5) the reduce of the
+    slots reproduces the reduced output. "zipf": the skewed-routing configuration (logit bias -2.2*ln(rank))."""
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(tokens)
+    xb, lg = orc.make_inputs(gen, tokens)
+    if kind == "zipf":
+        lg = lg - 2.2 * np.log(np.arange(1, 129, dtype=np.float32))[None, :]
+    x, logits = bf16_dev(xb), dev(lg)
+    slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+    out = C.mxfp4_moe(x, w, router_logits=logits)
+    wt, ids = C.route(x, w, router_logits=logits)
+    xq = C.mxfp4_quant(x)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert np.array_equal(ids.cpu().numpy(), orc.route_softmax(lg)[1])
+    assert np.array_equal(bits_of(out), orc.reduce_slots_bf16(bits_of(slots)))
+    assert torch.equal(slots, C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)[0])
+    # (1) sampled rows through the CUDA-core path
+    bm = C.variant_for(tokens)
+    sb = C.moe_sort(ids, wt, bm)
+    nv = int(sb.num_valid[0])
+    rows = torch.from_numpy(np.unique(np.random.default_rng(0).integers(0, nv, 96)).astype(np.int32)).cuda()
+    hq_r, sfh_r = C.simt_gemm1(xq, sb, w, rows)
+    slots_r = C.simt_gemm2(hq_r, sfh_r, sb, w, rows)
+    sid = sb.sorted_ids[rows.long()]
+    live = (sid & 0xFFFFFF) < tokens
+    tok, slot = (sid[live] & 0xFFFFFF).long(), (sid[live] >> 24).long()
+    a, b = slots[tok, slot].float().cpu().numpy(), slots_r[tok, slot].float().cpu().numpy()
+    assert cosine(a, b) >= 0.99999 and rel_l2(a, b) < 2e-3
+    # (2) CPU oracle on 16 tokens
+    pick = np.linspace(0, tokens - 1, 16).astype(int)
+    cpu = oracle_slots(xq[0].cpu().numpy(), xq[1].cpu().numpy(), raw, ids.cpu().numpy(), wt.cpu().numpy(), pick)
+    check_against_oracle(slots[torch.from_numpy(pick).cuda()].float().sum(1).cpu().numpy(), cpu.sum(1))
+    # (3) batch invariance
+    sel = torch.from_numpy(pick).cuda()
+    small, _ = C.mxfp4_moe(x[sel].contiguous(), w, router_logits=logits[sel].contiguous(), return_partials=True)
+    torch.cuda.synchronize()
+    assert torch.equal(small, slots[sel])
+
+
+def test_guard_bands_around_every_allocation(C, layer, monkeypatch):
+    """Every torch.empty of a call gets 128-byte guard bands and NaN / sentinel payloads (the reference's fixture,
+    tests/moe/.../test_entry.py:144-174): no kernel writes outside its buffers, and the outputs are fully written."""
+    import math
+    raw, w, _, _ = layer
+    for tokens in (1, 17, 129, 600):
+        gen = torch.Generator().manual_seed(tokens)
+        xb, lg = orc.make_inputs(gen, tokens)
+        x, logits = bf16_dev(xb), dev(lg)
+        real, guards = torch.empty, []
+
+        def guarded(*size, **kw):
+            dims = tuple(size[0]) if isinstance(size[0], (tuple, list, torch.Size)) else size
+            dtype = kw.get("dtype", torch.float32)
+            g = 512 // torch.tensor([], dtype=dtype).element_size()  # keeps the payload 512-byte aligned
+            store = real((math.prod(dims) + 2 * g,), **kw)
+            store.view(torch.uint8).fill_(17)
+            payload = store[g:-g].view(dims)
+            if dtype == torch.bfloat16:
+                payload.fill_(float("nan"))
+            guards.append((store, g))
+            return payload
+
+        with monkeypatch.context() as p:
+            p.setattr(torch, "empty", guarded)
+            out = C.mxfp4_moe(x, w, router_logits=logits)
+            slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+        torch.cuda.synchronize()
+        assert guards and torch.isfinite(out).all() and torch.isfinite(slots).all()
+        for store, g in guards:
+            raw_bytes = store.view(torch.uint8)
+            n = g * store.element_size()
+            assert bool((raw_bytes[:n] == 17).all()) and bool((raw_bytes[-n:] == 17).all())
+
+
+def test_results_identical_next_to_a_concurrent_kernel(C, layer):
+    raw, w, xb, lg = layer
+    x, logits = bf16_dev(xb), dev(lg)
+    expected = C.mxfp4_moe(x, w, router_logits=logits)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    a = torch.randn((4096, 4096), device="cuda", dtype=torch.bfloat16)
+    with torch.cuda.stream(side):
+        for _ in range(20):
+            a @ a
+    actual = C.mxfp4_moe(x, w, router_logits=logits)
+    torch.cuda.synchronize()
+    assert torch.equal(actual, expected) and C.last_status() == 0
+
+
+def test_entry_errors_and_warm_up(C, layer):
+    raw, w, xb, lg = layer
+    with pytest.raises(ValueError):
+        C.mxfp4_moe(torch.zeros((4, 6144), device="cuda"), w)
+    with pytest.raises(ValueError):
+        C.mxfp4_moe(torch.zeros((4, 6144), device="cuda", dtype=torch.bfloat16), w, router_logits=torch.zeros((4, 64), device="cuda"))
+    with pytest.raises(ValueError):
+        C.mxfp4_moe(torch.zeros((4, 6144), device="cuda", dtype=torch.bfloat16), w)  # no router weight, no logits
+    with pytest.raises(ValueError):
+        C.mxfp4_moe_experts((torch.zeros((0, 3072), dtype=torch.uint8, device="cuda"), None), None, None, w)
+    C.warm_up_mxfp4_moe(w, partials=True)
