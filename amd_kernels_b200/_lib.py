@@ -16,7 +16,7 @@ ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
 
 class Weights(Structure):
     """struct b200moe_weights"""
-    _fields_ = [("w13p", c_void_p), ("sf13p", c_void_p), ("w2", c_void_p), ("sf2p", c_void_p), ("bias", c_void_p),
+    _fields_ = [("w13t", c_void_p), ("w2t", c_void_p), ("bias", c_void_p),
                 ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float)]
 
 
@@ -26,15 +26,17 @@ SIGNATURES = {
     "b200moe_arch": (c_char_p, []),
     "b200moe_max_sorted_rows": (c_int64, [c_int64, c_int, c_int]),
     "b200moe_block_rows": (c_int, [c_int64]),
-    "b200moe_preshuffle_w13": (c_int, [_P, _P, c_int, _P, _P, _P]),
-    "b200moe_preshuffle_w2_scales": (c_int, [_P, c_int, _P, _P]),
+    "b200moe_preshuffle_w13": (c_int, [_P, _P, c_int, _P, _P]),
+    "b200moe_preshuffle_w2": (c_int, [_P, _P, c_int, _P, _P]),
     "b200moe_route_topk": (c_int, [_P, c_int64, c_int64, c_int, _P, c_int64, c_int, c_int, c_float, _P, _P, _P]),
     "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_permute": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
-    "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
-    "b200moe_gemm1_swiglu_quant": (c_int, [_P, _P, c_int, _P, _P, _P, _P, c_int64, c_int, _P, _P, _P, _P]),
-    "b200moe_gemm2_weighted": (c_int, [_P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_route_sort": (c_int, [_P, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P, _P, _P]),
+    "b200moe_quant_dispatch": (c_int, [_P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_gemm1_swiglu_quant": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, c_int, _P, _P, _P, _P]),
+    "b200moe_gemm2_weighted": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm1_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P]),
     "b200moe_reduce_slots": (c_int, [_P, _P, c_int64, _P, _P]),

@@ -8,8 +8,6 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Workspace {
   float* w;               // [T][4]
   int32_t* ids;           // [T][4]
-  uint8_t* codes;         // [T][3072]
-  uint8_t* scales;        // [T][192]
   int32_t* sorted_ids;    // [R]
   float* sorted_w;        // [R]
   int32_t* block_expert;  // [R/bm]
@@ -37,8 +35,6 @@ static Workspace carve(uint8_t* base, int64_t tokens, int num_experts) {
   };
   ws.w = reinterpret_cast<float*>(take(tokens * kTopK * 4));
   ws.ids = reinterpret_cast<int32_t*>(take(tokens * kTopK * 4));
-  ws.codes = take(tokens * (kH / 2));
-  ws.scales = take(tokens * (kH / 32));
   ws.sorted_ids = reinterpret_cast<int32_t*>(take(ws.rows * 4));
   ws.sorted_w = reinterpret_cast<float*>(take(ws.rows * 4));
   ws.block_expert = reinterpret_cast<int32_t*>(take(blocks * 4));
@@ -73,20 +69,17 @@ extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, con
   Workspace ws = carve(static_cast<uint8_t*>(workspace), tokens, ne);
   if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
   int r;
-  if ((r = b200moe_route_topk(logits, ne, 0, 1, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.w, ws.ids, stream)))
+  if ((r = b200moe_route_sort(logits, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.bm, ws.w, ws.ids,
+                              ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid, ws.scratch, stream)))
     return r;
-  if ((r = b200moe_quant_mxfp4(x_bf16, tokens, kH, ws.codes, ws.scales, stream))) return r;
-  if ((r = b200moe_permute(ws.ids, ws.w, tokens, ne, ws.bm, ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid,
-                           ws.scratch, stream)))
+  if ((r = b200moe_quant_dispatch(x_bf16, ws.sorted_ids, ws.num_valid, tokens, ws.bm, ws.rows, ws.xq_sorted, ws.sfx,
+                                  stream)))
     return r;
-  if ((r = b200moe_dispatch_rows(ws.codes, ws.scales, ws.sorted_ids, ws.num_valid, tokens, ws.bm, ws.rows, ws.xq_sorted,
-                                 ws.sfx, stream)))
+  if ((r = b200moe_gemm1_swiglu_quant(w->w13t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows, ws.bm,
+                                      ws.hq, ws.sfh, status, stream)))
     return r;
-  if ((r = b200moe_gemm1_swiglu_quant(w->w13p, w->sf13p, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows,
-                                      ws.bm, ws.hq, ws.sfh, status, stream)))
-    return r;
-  if ((r = b200moe_gemm2_weighted(w->w2, w->sf2p, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids,
-                                  ws.sorted_w, ws.rows, ws.bm, tokens, slots_bf16, status, stream)))
+  if ((r = b200moe_gemm2_weighted(w->w2t, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids, ws.sorted_w,
+                                  ws.rows, ws.bm, tokens, slots_bf16, status, stream)))
     return r;
   if (out_bf16 && (r = b200moe_reduce_slots(slots_bf16, nullptr, tokens, out_bf16, stream))) return r;
   return 0;

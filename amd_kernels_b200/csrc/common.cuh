@@ -18,6 +18,7 @@ constexpr int kW2Tiles = kH / 128;       // 48
 constexpr int kK1Tiles = kH / 256;       // 24 K-tiles (256 elements = 128 bytes) in GEMM1
 constexpr int kK2Tiles = kI / 256;       // 3 in GEMM2
 constexpr int kAtomBytes = 512;          // one scale atom
+constexpr int kTileRecordBytes = 128 * 128 + 2 * kAtomBytes;  // one weight tile (swizzled codes + scales) in HBM
 
 #define B200MOE_CHECK_LAUNCH()                        \
   do {                                                \
@@ -55,7 +56,7 @@ __device__ __forceinline__ uint32_t e2m1_code(float v, int e) {
 __device__ __forceinline__ float swiglu_oai(float g, float u) {
   g = fminf(g, 7.0f);
   u = fminf(fmaxf(u, -7.0f), 7.0f);
-  const float sig = 1.0f / (1.0f + __expf(-1.702f * g));
+  const float sig = __fdividef(1.0f, 1.0f + __expf(-1.702f * g));  // exp2 + rcp approximations, as the reference kernels
   return g * sig * (u + 1.0f);
 }
 

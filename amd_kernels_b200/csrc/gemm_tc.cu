@@ -131,17 +131,25 @@ struct Cfg {
   static constexpr int kTilesM = MODE == 1 ? kW13Tiles : kW2Tiles;
   static constexpr int kTilesK = MODE == 1 ? kK1Tiles : kK2Tiles;
   static constexpr int kABytes = 128 * 128;
-  static constexpr int kBBytes = BM * 128;
   static constexpr int kSfBytes = 2 * kAtomBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
-  static constexpr int kStages = BM == 128 ? 6 : (BM == 64 ? 7 : 8);
+  static constexpr int kBBytes = BM * 128;
+  // stage = [weight tile record: codes | scales][activation codes][activation scales]
+  static constexpr int kBOffset = kTileRecordBytes;
+  static constexpr int kSfbOffset = kBOffset + kBBytes;
+  static constexpr int kStageBytes = kSfbOffset + kSfBytes;
+  static constexpr int kStages = MODE == 1 ? (BM == 128 ? 5 : (BM == 64 ? 6 : 8)) : (BM == 128 ? 6 : 8);
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   static constexpr int kSfaCol = 2 * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
   static constexpr int kColsUsed = kSfbCol + 8;
   static constexpr int kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the first tile to 1024 bytes
+  // GEMM1 epilogue staging: up to 64 token columns x (2 groups x (32 gate + 32 up + 4 pad)) floats
+  static constexpr int kEpiCols = BM < 64 ? BM : 64;
+  static constexpr int kEpiRowFloats = 136;
+  static constexpr int kEpiBytes = MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;  // + slack to align to 1024 bytes
   static constexpr int kActAtomsPerBlock = MODE == 1 ? kH / 128 : kI / 128;  // activation scale atoms per row block
+  static constexpr int kActRowBytes = MODE == 1 ? kH / 2 : kI / 2;
 };
 
 struct EpilogueArgs {
@@ -157,12 +165,18 @@ struct EpilogueArgs {
 
 constexpr int kThreads = 192;
 
+// two E2M1 codes in one byte: `lo` in the low nibble, `hi` in the high nibble; round to nearest even, saturating
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+  uint16_t out;
+  asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u16.u8 %0, t;\n}\n" : "=h"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+
 template <int MODE, int BM>
 __global__ void __launch_bounds__(kThreads, 1)
-    grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                        const uint8_t* __restrict__ sf_w, const uint8_t* __restrict__ sf_x,
-                        const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid,
-                        EpilogueArgs ep, int32_t* status) {
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
+                        const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
+                        const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status) {
   using C = Cfg<MODE, BM>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
@@ -171,7 +185,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float exch[MODE == 1 ? 2 : 1][2][16][32];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -212,8 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const int b = u / C::kTilesM, mt = u % C::kTilesM;
         const int e = block_expert[b];
-        const int w_row = (e * C::kTilesM + mt) * 128;
-        const uint8_t* sfa_src = sf_w + static_cast<int64_t>(e * C::kTilesM + mt) * C::kTilesK * C::kSfBytes;
+        const uint8_t* w_src = w_tiles + static_cast<int64_t>(e * C::kTilesM + mt) * C::kTilesK * kTileRecordBytes;
         const uint8_t* sfb_src = sf_x + static_cast<int64_t>(b) * C::kActAtomsPerBlock * kAtomBytes;
         for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
@@ -221,10 +233,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t base = tiles + s * C::kStageBytes;
           mbar_arrive_expect_tx(full, C::kStageBytes);
-          tma_load_2d(base, &map_w, kt * 128, w_row, full);
-          tma_load_2d(base + C::kABytes, &map_x, kt * 128, b * BM, full);
-          bulk_load(base + C::kABytes + C::kBBytes, sfa_src + kt * C::kSfBytes, C::kSfBytes, full);
-          bulk_load(base + C::kABytes + C::kBBytes + C::kSfBytes, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
+          bulk_load(base, w_src + static_cast<int64_t>(kt) * kTileRecordBytes, kTileRecordBytes, full);
+          tma_load_2d(base + C::kBOffset, &map_x, kt * 128, b * BM, full);
+          bulk_load(base + C::kSfbOffset, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
         }
       }
       if (!ok) {
@@ -253,12 +264,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t base = tiles + s * C::kStageBytes;
-          const uint32_t sfa = base + C::kABytes + C::kBBytes, sfb = sfa + C::kSfBytes;
+          const uint32_t sfa = base + C::kABytes, sfb = base + C::kSfbOffset;
           tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(sfa));
           tc_cp_scales(tmem_base + C::kSfaCol + 4, scale_desc(sfa + kAtomBytes));
           tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(sfb));
           tc_cp_scales(tmem_base + C::kSfbCol + 4, scale_desc(sfb + kAtomBytes));
-          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kABytes);
+          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // 64 elements = 32 bytes per MMA; scales: atom k/2, bytes {0,1} or {2,3} of each row's 4-byte cell
@@ -275,61 +286,100 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, TMEM lane quarter = warp % 4)
     const int q = warp & 3;
-    uint32_t ui = 0, chunk_no = 0;
+    const int et = threadIdx.x - 64;  // 0..127
+    float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + C::kStages * C::kStageBytes);
+    uint32_t ui = 0;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+      const int64_t row0 = static_cast<int64_t>(b) * BM;
+      int sid[(BM + 31) / 32];
+      float wt[(BM + 31) / 32];
+      if (MODE == 2) {
+#pragma unroll
+        for (int r = 0; r < (BM + 31) / 32; ++r) {
+          const int row = r * 32 + lane;
+          sid[r] = row < BM ? __ldg(ep.sorted_ids + row0 + row) : 0x00ffffff;
+          wt[r] = row < BM ? __ldg(ep.sorted_w + row0 + row) : 0.0f;
+        }
+      }
       // the four warps must agree before they meet at the named barrier below
       if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status))) break;
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
-      const int64_t row0 = static_cast<int64_t>(b) * BM;
+      if (MODE == 1) {
+        // TMEM lanes of a tile: quarter 0 = gate i 0..31, 1 = up i 0..31, 2 = gate i 32..63, 3 = up i 32..63.
+        // Stage the accumulators as [token][group][32 gate | 32 up | pad] so one thread owns one (token, 32-column
+        // group): SwiGLU, the block maximum and the 32 codes are thread-local and the codes leave as one 16-byte store.
+        float* mine = stage_f + (q >> 1) * 68 + (q & 1) * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BM / 16; ++c, ++chunk_no) {
-        uint32_t v[16];
-        tc_ld16(t_acc + c * 16, v);
-        if (MODE == 1) {
-          float(*ex)[32] = exch[chunk_no & 1][q >> 1];
-          if (q & 1) {
+        for (int c0 = 0; c0 < BM; c0 += C::kEpiCols) {
+#pragma unroll 1
+          for (int cc = 0; cc < C::kEpiCols; cc += 16) {
+            uint32_t v[16];
+            tc_ld16(t_acc + c0 + cc, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ex[j][lane] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) mine[(cc + j) * C::kEpiRowFloats] = __uint_as_float(v[j]);
+          }
+          if (c0 + C::kEpiCols >= BM) {  // accumulator fully read: hand the TMEM buffer back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (!(q & 1)) {
-            const int g = 2 * mt + (q >> 1);  // 32-column group of the intermediate, 0..23
+          for (int item = et; item < 2 * C::kEpiCols; item += 128) {
+            const int j = item >> 1, g = item & 1;
+            const float4* src = reinterpret_cast<const float4*>(stage_f + j * C::kEpiRowFloats + g * 68);
+            float h[32];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int n = c * 16 + j;
-              const float h = swiglu_oai(__uint_as_float(v[j]), ex[j][lane]);
-              const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h))));
-              const int sc = quark_even_e8m0(amax);
-              uint32_t code = e2m1_code(h, sc);
-              code |= __shfl_down_sync(0xffffffffu, code, 1) << 4;
-              code |= __shfl_down_sync(0xffffffffu, code, 2) << 8;
-              code |= __shfl_down_sync(0xffffffffu, code, 4) << 16;
-              if ((lane & 7) == 0)
-                *reinterpret_cast<uint32_t*>(ep.hq + (row0 + n) * (kI / 2) + g * 16 + (lane >> 3) * 4) = code;
-              if (lane == 0)
-                ep.sfh[(static_cast<int64_t>(b) * (kI / 128) + (g >> 2)) * kAtomBytes + atom_offset(n, g & 3)] =
-                    static_cast<uint8_t>(sc);
+            for (int k = 0; k < 8; ++k) {
+              const float4 gv = src[k], uv = src[8 + k];
+              h[4 * k + 0] = swiglu_oai(gv.x, uv.x);
+              h[4 * k + 1] = swiglu_oai(gv.y, uv.y);
+              h[4 * k + 2] = swiglu_oai(gv.z, uv.z);
+              h[4 * k + 3] = swiglu_oai(gv.w, uv.w);
             }
+            float amax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) amax = fmaxf(amax, fabsf(h[k]));
+            const int sc = quark_even_e8m0(amax);
+            const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
+            uint32_t words[4];
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd) {
+              uint32_t acc_w = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
+              words[wd] = acc_w;
+            }
+            const int grp = 2 * mt + g;  // 32-column group of the intermediate, 0..23
+            const int n = c0 + j;
+            *reinterpret_cast<uint4*>(ep.hq + (row0 + n) * (kI / 2) + grp * 16) =
+                make_uint4(words[0], words[1], words[2], words[3]);
+            ep.sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(n, grp & 3)] =
+                static_cast<uint8_t>(sc);
           }
-        } else {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BM / 16; ++c) {
+          uint32_t v[16];
+          tc_ld16(t_acc + c * 16, v);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int64_t row = row0 + c * 16 + j;
-            const int sid = __ldg(ep.sorted_ids + row);
-            const int64_t token = sid & 0x00ffffff;
-            if (token < ep.tokens) {
-              const float wt = __ldg(ep.sorted_w + row);
-              ep.slots[(token * kTopK + (sid >> 24)) * kH + mt * 128 + q * 32 + lane] =
-                  __float2bfloat16_rn(__uint_as_float(v[j]) * wt);
-            }
+            const int col = c * 16 + j;
+            const int s_id = __shfl_sync(0xffffffffu, sid[col >> 5], col & 31);
+            const float s_w = __shfl_sync(0xffffffffu, wt[col >> 5], col & 31);
+            const int64_t token = s_id & 0x00ffffff;
+            if (token < ep.tokens)
+              ep.slots[(token * kTopK + (s_id >> 24)) * kH + mt * 128 + q * 32 + lane] =
+                  __float2bfloat16_rn(__uint_as_float(v[j]) * s_w);
           }
         }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_tempty[acc]));
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bar_tempty[acc]));
     }
   }
 
@@ -385,7 +435,7 @@ static int sm_count() {
 }
 
 template <int MODE, int BM>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const uint8_t* sf_w, const uint8_t* sf_x,
+static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
                   int32_t* status, cudaStream_t stream) {
   using C = Cfg<MODE, BM>;
@@ -399,21 +449,21 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const uint8_t* s
   const int64_t max_units = max_rows / BM * C::kTilesM;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   if (grid <= 0) return 0;
-  grouped_gemm_kernel<MODE, BM><<<grid, kThreads, C::kSmemBytes, stream>>>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep,
+  grouped_gemm_kernel<MODE, BM><<<grid, kThreads, C::kSmemBytes, stream>>>(mx, w_tiles, sf_x, block_expert, num_valid, ep,
                                                                           status);
   B200MOE_CHECK_LAUNCH();
   return 0;
 }
 
 template <int MODE>
-static int launch_bm(int bm, const CUtensorMap& mw, const CUtensorMap& mx, const uint8_t* sf_w, const uint8_t* sf_x,
+static int launch_bm(int bm, const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                      const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
                      int32_t* status, cudaStream_t stream) {
   switch (bm) {
-    case 16: return launch<MODE, 16>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 32: return launch<MODE, 32>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 64: return launch<MODE, 64>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 128: return launch<MODE, 128>(mw, mx, sf_w, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 16: return launch<MODE, 16>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 32: return launch<MODE, 32>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 64: return launch<MODE, 64>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 128: return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
   }
   return B200MOE_E_ARG;
 }
@@ -422,56 +472,49 @@ static bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<ui
 
 }  // namespace b200moe
 
-extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13p, const uint8_t* sf13p, int num_experts,
-                                          const uint8_t* xq_sorted, const uint8_t* sfx, const int32_t* block_expert,
-                                          const int32_t* num_valid, int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh,
-                                          int32_t* status, void* stream) {
+extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted,
+                                          const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
+                                          int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh, int32_t* status,
+                                          void* stream) {
   using namespace b200moe;
-  if (!w13p || !sf13p || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status)
-    return B200MOE_E_ARG;
+  if (!w13t || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status) return B200MOE_E_ARG;
   if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || (bm != 16 && bm != 32 && bm != 64 && bm != 128) ||
       max_rows % bm)
     return B200MOE_E_ARG;
-  if (misaligned(w13p, 16) || misaligned(sf13p, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) ||
-      misaligned(hq, 16) || misaligned(sfh, 16))
+  if (misaligned(w13t, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) || misaligned(hq, 16) ||
+      misaligned(sfh, 16))
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
-  CUtensorMap mw, mx;
-  int r = make_map(&mw, w13p, kH / 2, static_cast<uint64_t>(num_experts) * 2 * kI, 128);
-  if (r) return r;
-  r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  CUtensorMap mx;
+  const int r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
   if (r) return r;
   EpilogueArgs ep{};
   ep.hq = hq;
   ep.sfh = sfh;
-  return launch_bm<1>(bm, mw, mx, sf13p, sfx, block_expert, num_valid, ep, max_rows, status,
+  return launch_bm<1>(bm, mx, w13t, sfx, block_expert, num_valid, ep, max_rows, status,
                       static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int b200moe_gemm2_weighted(const uint8_t* w2, const uint8_t* sf2p, int num_experts, const uint8_t* hq,
-                                      const uint8_t* sfh, const int32_t* block_expert, const int32_t* num_valid,
-                                      const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm,
-                                      int64_t tokens, void* slots_bf16, int32_t* status, void* stream) {
+extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                      const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                                      const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
+                                      int32_t* status, void* stream) {
   using namespace b200moe;
-  if (!w2 || !sf2p || !hq || !sfh || !block_expert || !num_valid || !sorted_ids || !sorted_w || !slots_bf16 || !status)
+  if (!w2t || !hq || !sfh || !block_expert || !num_valid || !sorted_ids || !sorted_w || !slots_bf16 || !status)
     return B200MOE_E_ARG;
   if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || tokens < 0 ||
       (bm != 16 && bm != 32 && bm != 64 && bm != 128) || max_rows % bm)
     return B200MOE_E_ARG;
-  if (misaligned(w2, 16) || misaligned(sf2p, 16) || misaligned(hq, 16) || misaligned(sfh, 16))
-    return B200MOE_E_ALIGN;
+  if (misaligned(w2t, 16) || misaligned(hq, 16) || misaligned(sfh, 16)) return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
-  CUtensorMap mw, mx;
-  int r = make_map(&mw, w2, kI / 2, static_cast<uint64_t>(num_experts) * kH, 128);
-  if (r) return r;
-  r = make_map(&mx, hq, kI / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  CUtensorMap mx;
+  const int r = make_map(&mx, hq, kI / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
   if (r) return r;
   EpilogueArgs ep{};
   ep.sorted_ids = sorted_ids;
   ep.sorted_w = sorted_w;
   ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
   ep.tokens = tokens;
-  return launch_bm<2>(bm, mw, mx, sf2p, sfh, block_expert, num_valid, ep, max_rows, status,
+  return launch_bm<2>(bm, mx, w2t, sfh, block_expert, num_valid, ep, max_rows, status,
                       static_cast<cudaStream_t>(stream));
 }
-

@@ -38,13 +38,15 @@ __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __res
                                                             const uint8_t* __restrict__ scales,
                                                             const int32_t* __restrict__ sorted_ids,
                                                             const int32_t* __restrict__ num_valid, int64_t tokens,
-                                                            int bm, uint8_t* __restrict__ xq_sorted,
+                                                            int bm, int by_pair, uint8_t* __restrict__ xq_sorted,
                                                             uint8_t* __restrict__ sfx) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= num_valid[0]) return;
-  const int64_t token = sorted_ids[row] & 0x00ffffff;
-  const bool pad = token >= tokens;
+  const int sid = sorted_ids[row];
+  const bool pad = (sid & 0x00ffffff) >= tokens;
+  // source row: the token, or (by_pair) the pair 4*token+slot when every (token, slot) carries its own quantised row
+  const int64_t token = by_pair ? static_cast<int64_t>(sid & 0x00ffffff) * kTopK + (sid >> 24) : (sid & 0x00ffffff);
   uint4* dst = reinterpret_cast<uint4*>(xq_sorted + row * (kH / 2));
   const uint4* src = reinterpret_cast<const uint4*>(codes + token * (kH / 2));
 #pragma unroll
@@ -56,6 +58,51 @@ __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __res
   uint8_t* sdst = sfx + block * (kH / 128) * kAtomBytes + atom_offset(r, 0);
   for (int a = lane; a < kH / 128; a += 32)
     *reinterpret_cast<uint32_t*>(sdst + a * kAtomBytes) = pad ? 0x7f7f7f7fu : ssrc[a];
+}
+
+// Quantisation fused with the gather: one warp per sorted row reads the token's bf16 row, quantises it and writes the
+// codes in sorted order and the scales into the block's atoms (a token is quantised once per slot; the reads hit L2).
+__global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __restrict__ x,
+                                                             const int32_t* __restrict__ sorted_ids,
+                                                             const int32_t* __restrict__ num_valid, int64_t tokens,
+                                                             int bm_shift, uint8_t* __restrict__ xq_sorted,
+                                                             uint8_t* __restrict__ sfx) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= num_valid[0]) return;
+  const int64_t token = sorted_ids[row] & 0x00ffffff;
+  const bool pad = token >= tokens;
+  const uint4* src = x + token * (kH / 8);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + row * (kH / 2));
+  const int r = static_cast<int>(row & ((1 << bm_shift) - 1));
+  uint8_t* sdst = sfx + (row >> bm_shift) * (kH / 128) * kAtomBytes + atom_offset(r, 0);
+#pragma unroll 4
+  for (int it = 0; it < kH / 8 / 32; ++it) {
+    const int idx = it * 32 + lane;
+    const uint4 raw = pad ? make_uint4(0, 0, 0, 0) : src[idx];
+    const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(rr[j] << 16);
+      v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const int e = quark_even_e8m0(amax);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) packed |= e2m1_code(v[j], e) << (4 * j);
+    dst[idx] = packed;
+    // 8 blocks of 32 per warp step = 2 atoms' worth of 4 scale bytes: lanes 0 and 16 gather 4 neighbours' bytes
+    uint32_t sc = static_cast<uint32_t>(e);
+    sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
+    sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
+    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (it * 2 + (lane >> 4)) * kAtomBytes) = sc;
+  }
 }
 
 }  // namespace b200moe
@@ -75,7 +122,7 @@ extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, ui
 }
 
 extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
-                                     const int32_t* num_valid, int64_t tokens, int bm, int64_t max_rows,
+                                     const int32_t* num_valid, int64_t tokens, int bm, int by_pair, int64_t max_rows,
                                      uint8_t* xq_sorted, uint8_t* sfx, void* stream) {
   using namespace b200moe;
   if (!codes || !scales || !sorted_ids || !num_valid || !xq_sorted || !sfx || tokens < 0 || max_rows < 0)
@@ -87,7 +134,25 @@ extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales
   if (max_rows == 0) return 0;
   const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
   dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, scales, sorted_ids, num_valid,
-                                                                            tokens, bm, xq_sorted, sfx);
+                                                                            tokens, bm, by_pair, xq_sorted, sfx);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid,
+                                      int64_t tokens, int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
+                                      void* stream) {
+  using namespace b200moe;
+  if (!x_bf16 || !sorted_ids || !num_valid || !xq_sorted || !sfx || tokens < 0 || max_rows < 0) return B200MOE_E_ARG;
+  const int shift = bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1;
+  if (shift < 0) return B200MOE_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(xq_sorted) & 15) ||
+      (reinterpret_cast<uintptr_t>(sfx) & 15))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
+  quant_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx);
   B200MOE_CHECK_LAUNCH();
   return 0;
 }

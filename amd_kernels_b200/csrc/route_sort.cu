@@ -1,0 +1,365 @@
+// Router top-4 and the routing sort (a stable counting sort of the 4T (token, slot) pairs by expert with per-expert
+// padding to bm rows). For T <= 256 both run in ONE single-CTA kernel; above that the router is its own grid and the
+// sort runs as a count pass and a placement pass over 1024-pair chunks.
+//
+// Determinism: counts are order-free; placement ranks come from warp match/popc and fixed-order prefix sums, so the row
+// order inside an expert is the pair order 4*token+slot on every run.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kChunk = 1024;
+
+// (value, id) ordering: larger value first, equal values to the lower id.
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+// One warp routes one token. Lane owns experts lane, lane+32, lane+64, lane+96. Every lane returns the 4 picks.
+template <int MODE>
+__device__ __forceinline__ void route_token(const float* __restrict__ row, int64_t stride_s, int splits,
+                                            const float* __restrict__ bias, int num_experts, float scale, int lane,
+                                            float (&w)[4], int (&sel_id)[4]) {
+  float score[4], choice[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = lane + 32 * j;
+    float acc = 0.0f;
+    if (e < num_experts)
+      for (int s = 0; s < splits; ++s) acc = acc + row[s * stride_s + e];
+    if (MODE == B200MOE_ROUTE_SIGMOID_BIAS) {
+      score[j] = 1.0f / (1.0f + expf(-acc));
+      choice[j] = score[j] + (bias && e < num_experts ? bias[e] : 0.0f);
+    } else {
+      score[j] = acc;
+      choice[j] = acc;
+    }
+    if (e >= num_experts) choice[j] = -INFINITY;
+  }
+  float sel_score[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    float bv = -INFINITY, bs = 0.0f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = lane + 32 * j;
+      if (e < num_experts && better(choice[j], e, bv, bi)) { bv = choice[j]; bi = e; bs = score[j]; }
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      const float os = __shfl_xor_sync(0xffffffffu, bs, off);
+      if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; bs = os; }
+    }
+    if (bi == 0x7fffffff) { bi = r; bs = 0.0f; }  // nothing comparable left (a NaN row): the round number
+    sel_id[r] = bi;
+    sel_score[r] = bs;
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j == (bi >> 5)) choice[j] = -INFINITY;
+    }
+  }
+  if (MODE == B200MOE_ROUTE_SIGMOID_BIAS) {
+    const float sum = ((sel_score[0] + sel_score[1]) + sel_score[2]) + sel_score[3];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) w[r] = sel_score[r] * scale / sum;
+  } else {
+    float p[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) p[r] = expf(sel_score[r] - sel_score[0]);
+    const float sum = ((p[0] + p[1]) + p[2]) + p[3];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) w[r] = p[r] * scale / sum;
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ partials, int64_t stride_t,
+                                                         int64_t stride_s, int splits, const float* __restrict__ bias,
+                                                         int64_t tokens, int num_experts, float scale,
+                                                         float* __restrict__ out_w, int32_t* __restrict__ out_ids) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  float w[4];
+  int id[4];
+  route_token<MODE>(partials + t * stride_t, stride_s, splits, bias, num_experts, scale, lane, w, id);
+  if (lane < 4) {
+    float wv = w[0];
+    int iv = id[0];
+#pragma unroll
+    for (int r = 1; r < 4; ++r)
+      if (lane == r) { wv = w[r]; iv = id[r]; }
+    out_w[t * 4 + lane] = wv;
+    out_ids[t * 4 + lane] = iv;
+  }
+}
+
+__global__ void __launch_bounds__(kChunk) permute_count_kernel(const int32_t* __restrict__ ids, int64_t pairs,
+                                                               int num_experts, int32_t* __restrict__ cta_counts) {
+  __shared__ int hist[kMaxE];
+  if (threadIdx.x < kMaxE) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
+  if (q < pairs) {
+    const int e = ids[q];
+    if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < num_experts) cta_counts[static_cast<int64_t>(blockIdx.x) * num_experts + threadIdx.x] = hist[threadIdx.x];
+}
+
+struct SortShared {
+  int total[kMaxE];        // pairs per expert over the whole call
+  int base[kMaxE];         // pairs of this expert in earlier chunks
+  int start[kMaxE + 4];    // first padded row of each expert, [num_experts] = padded total
+  int warp_cnt[32][kMaxE + 1];
+};
+
+// The placement of one 1024-pair chunk. e = this thread's expert (or -1), wv its routing weight, q its pair index.
+__device__ __forceinline__ void place_chunk(SortShared& sh, int e, float wv, int64_t q, int64_t tokens, int num_experts,
+                                            int bm_shift, const int32_t* __restrict__ cta_counts,
+                                            int32_t* __restrict__ sorted_ids, float* __restrict__ sorted_w,
+                                            int32_t* __restrict__ block_expert, int32_t* __restrict__ num_valid) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bm = 1 << bm_shift;
+  for (int i = tid; i < 32 * (kMaxE + 1); i += kChunk) (&sh.warp_cnt[0][0])[i] = 0;
+  if (tid < kMaxE) { sh.total[tid] = 0; sh.base[tid] = 0; }
+  __syncthreads();
+  // rank inside the warp, and the warp's count per expert
+  const unsigned live = __ballot_sync(0xffffffffu, e >= 0);
+  int rank = 0;
+  if (e >= 0) {
+    const unsigned peers = __match_any_sync(live, e);
+    rank = __popc(peers & ((1u << lane) - 1u));
+    if (rank == 0) sh.warp_cnt[warp][e] = __popc(peers);
+  }
+  __syncthreads();
+  if (tid < num_experts) {
+    // exclusive prefix over the warps of this chunk in warp order; totals and the base of earlier chunks
+    int run = 0;
+#pragma unroll 8
+    for (int wi = 0; wi < 32; ++wi) {
+      const int n = sh.warp_cnt[wi][tid];
+      sh.warp_cnt[wi][tid] = run;
+      run += n;
+    }
+    int t = run, b = 0;
+    if (cta_counts != nullptr) {
+      t = 0;
+      for (unsigned c = 0; c < gridDim.x; ++c) {
+        const int n = cta_counts[static_cast<int64_t>(c) * num_experts + tid];
+        if (c < blockIdx.x) b += n;
+        t += n;
+      }
+    }
+    sh.total[tid] = t;
+    sh.base[tid] = b;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // padded sizes and their exclusive scan over the experts: lane owns experts 4*lane .. 4*lane+3
+    int pad[4], sum = 0, last = -1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int x = 4 * lane + j;
+      const int t = x < num_experts ? sh.total[x] : 0;
+      pad[j] = ((t + bm - 1) >> bm_shift) << bm_shift;
+      sum += pad[j];
+      if (t > 0) last = x;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sh.start[4 * lane + j] = run;
+      run += pad[j];
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+    const int grand = __shfl_sync(0xffffffffu, incl, 31);
+    __syncwarp();
+    if (lane == 0) {
+      sh.start[num_experts] = grand;  // experts beyond num_experts have zero size, so start[num_experts] == total
+      if (blockIdx.x == 0) {
+        num_valid[0] = grand;
+        num_valid[1] = last >= 0 ? sh.start[last] : 0;
+      }
+    }
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int pos = sh.start[e] + sh.base[e] + sh.warp_cnt[warp][e] + rank;
+    sorted_ids[pos] = static_cast<int>(q >> 2) | (static_cast<int>(q & 3) << 24);
+    sorted_w[pos] = wv;
+  }
+  // padding rows and the block -> expert list: experts dealt round-robin to the chunks, then to the warps
+  for (int x = blockIdx.x + warp * gridDim.x; x < num_experts; x += 32 * gridDim.x) {
+    const int first = sh.start[x], live_rows = sh.total[x];
+    const int padded = (((live_rows + bm - 1) >> bm_shift) << bm_shift);
+    for (int r = live_rows + lane; r < padded; r += 32) {
+      sorted_ids[first + r] = static_cast<int>(tokens);
+      sorted_w[first + r] = 0.0f;
+    }
+    for (int b = lane; b < (padded >> bm_shift); b += 32) block_expert[(first >> bm_shift) + b] = x;
+  }
+}
+
+__global__ void __launch_bounds__(kChunk) permute_place_kernel(const int32_t* __restrict__ ids,
+                                                               const float* __restrict__ w, int64_t tokens,
+                                                               int num_experts, int bm_shift,
+                                                               const int32_t* __restrict__ cta_counts,
+                                                               int32_t* __restrict__ sorted_ids,
+                                                               float* __restrict__ sorted_w,
+                                                               int32_t* __restrict__ block_expert,
+                                                               int32_t* __restrict__ num_valid) {
+  __shared__ SortShared sh;
+  const int64_t pairs = tokens * kTopK;
+  const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
+  int e = -1;
+  float wv = 0.0f;
+  if (q < pairs) {
+    e = ids[q];
+    wv = w[q];
+    if (e < 0 || e >= num_experts) e = -1;
+  }
+  place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, cta_counts, sorted_ids, sorted_w, block_expert, num_valid);
+}
+
+// T <= 256: routing and the sort in one CTA. Warp w routes tokens w, w+32, ...
+template <int MODE>
+__global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restrict__ logits,
+                                                            const float* __restrict__ bias, int tokens,
+                                                            int num_experts, float scale, int bm_shift,
+                                                            float* __restrict__ out_w, int32_t* __restrict__ out_ids,
+                                                            int32_t* __restrict__ sorted_ids,
+                                                            float* __restrict__ sorted_w,
+                                                            int32_t* __restrict__ block_expert,
+                                                            int32_t* __restrict__ num_valid) {
+  __shared__ SortShared sh;
+  __shared__ int s_ids[kChunk];
+  __shared__ float s_w[kChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int t = warp; t < tokens; t += 32) {
+    float w[4];
+    int id[4];
+    route_token<MODE>(logits + static_cast<int64_t>(t) * num_experts, 0, 1, bias, num_experts, scale, lane, w, id);
+    if (lane < 4) {
+      float wv = w[0];
+      int iv = id[0];
+#pragma unroll
+      for (int r = 1; r < 4; ++r)
+        if (lane == r) { wv = w[r]; iv = id[r]; }
+      s_ids[t * 4 + lane] = iv;
+      s_w[t * 4 + lane] = wv;
+      out_w[t * 4 + lane] = wv;
+      out_ids[t * 4 + lane] = iv;
+    }
+  }
+  __syncthreads();
+  const int q = threadIdx.x;
+  int e = -1;
+  float wv = 0.0f;
+  if (q < tokens * kTopK) { e = s_ids[q]; wv = s_w[q]; }
+  place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, nullptr, sorted_ids, sorted_w, block_expert, num_valid);
+}
+
+static int shift_of(int bm) { return bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1; }
+
+}  // namespace b200moe
+
+extern "C" int b200moe_route_topk(const float* partials, int64_t stride_t, int64_t stride_s, int splits,
+                                  const float* bias, int64_t tokens, int num_experts, int mode, float scale,
+                                  float* out_w, int32_t* out_ids, void* stream) {
+  using namespace b200moe;
+  if (!partials || !out_w || !out_ids || tokens < 0 || splits < 1 || num_experts < 4 || num_experts > kMaxE)
+    return B200MOE_E_ARG;
+  if (mode != B200MOE_ROUTE_SIGMOID_BIAS && mode != B200MOE_ROUTE_SOFTMAX) return B200MOE_E_ARG;
+  if (tokens == 0) return 0;
+  const int warps = 8;
+  const unsigned grid = static_cast<unsigned>((tokens + warps - 1) / warps);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (mode == B200MOE_ROUTE_SIGMOID_BIAS)
+    route_topk_kernel<B200MOE_ROUTE_SIGMOID_BIAS><<<grid, warps * 32, 0, s>>>(partials, stride_t, stride_s, splits, bias,
+                                                                             tokens, num_experts, scale, out_w, out_ids);
+  else
+    route_topk_kernel<B200MOE_ROUTE_SOFTMAX><<<grid, warps * 32, 0, s>>>(partials, stride_t, stride_s, splits, bias,
+                                                                        tokens, num_experts, scale, out_w, out_ids);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts) {
+  const int64_t chunks = (tokens * b200moe::kTopK + b200moe::kChunk - 1) / b200moe::kChunk;
+  return chunks > 1 ? static_cast<size_t>(chunks) * num_experts * sizeof(int32_t) : 0;
+}
+
+extern "C" int64_t b200moe_max_sorted_rows(int64_t tokens, int bm, int num_experts) {
+  const int64_t pairs = tokens * b200moe::kTopK;
+  const int64_t ex = pairs < num_experts ? pairs : num_experts;
+  return (pairs + ex * (bm - 1) + bm - 1) / bm * bm;
+}
+
+extern "C" int b200moe_block_rows(int64_t tokens) {
+  if (tokens <= 128) return 16;
+  if (tokens <= 512) return 32;
+  if (tokens <= 1024) return 64;
+  return 128;
+}
+
+extern "C" int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
+                               int32_t* sorted_ids, float* sorted_w, int32_t* block_expert, int32_t* num_valid,
+                               int32_t* scratch, void* stream) {
+  using namespace b200moe;
+  if (!ids || !w || !sorted_ids || !sorted_w || !block_expert || !num_valid) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
+  const int shift = shift_of(bm);
+  if (shift < 0) return B200MOE_E_ARG;
+  const int64_t pairs = tokens * kTopK;
+  const unsigned chunks = static_cast<unsigned>((pairs + kChunk - 1) / kChunk);
+  if (chunks > 1 && !scratch) return B200MOE_E_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (chunks > 1) {
+    permute_count_kernel<<<chunks, kChunk, 0, s>>>(ids, pairs, num_experts, scratch);
+    B200MOE_CHECK_LAUNCH();
+  }
+  permute_place_kernel<<<chunks, kChunk, 0, s>>>(ids, w, tokens, num_experts, shift, chunks > 1 ? scratch : nullptr,
+                                                 sorted_ids, sorted_w, block_expert, num_valid);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, int num_experts, int mode,
+                                  float scale, int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids,
+                                  float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch,
+                                  void* stream) {
+  using namespace b200moe;
+  if (!logits || !out_w || !out_ids || !sorted_ids || !sorted_w || !block_expert || !num_valid) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 4 || num_experts > kMaxE) return B200MOE_E_ARG;
+  if (mode != B200MOE_ROUTE_SIGMOID_BIAS && mode != B200MOE_ROUTE_SOFTMAX) return B200MOE_E_ARG;
+  const int shift = shift_of(bm);
+  if (shift < 0) return B200MOE_E_ARG;
+  if (tokens * kTopK > kChunk) {
+    int r = b200moe_route_topk(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, out_w, out_ids, stream);
+    if (r) return r;
+    return b200moe_permute(out_ids, out_w, tokens, num_experts, bm, sorted_ids, sorted_w, block_expert, num_valid, scratch,
+                           stream);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (mode == B200MOE_ROUTE_SIGMOID_BIAS)
+    route_sort_kernel<B200MOE_ROUTE_SIGMOID_BIAS><<<1, kChunk, 0, s>>>(logits, bias, static_cast<int>(tokens), num_experts,
+                                                                      scale, shift, out_w, out_ids, sorted_ids, sorted_w,
+                                                                      block_expert, num_valid);
+  else
+    route_sort_kernel<B200MOE_ROUTE_SOFTMAX><<<1, kChunk, 0, s>>>(logits, bias, static_cast<int>(tokens), num_experts,
+                                                                 scale, shift, out_w, out_ids, sorted_ids, sorted_w,
+                                                                 block_expert, num_valid);
+  B200MOE_CHECK_LAUNCH();
+  return 0;
+}

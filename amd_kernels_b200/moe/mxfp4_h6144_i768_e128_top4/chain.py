@@ -58,14 +58,16 @@ class MoeWeights:
     """The router (fp32 [E, H]) and bias (fp32 [E]), and the experts in the kernels' layouts, built once by
     ``from_row_major`` before graph capture (reference chain.py:23-50).
 
-    ``w13`` [E, 12, 128, 3072] u8: tiles of 64 gate + 64 up rows in 32-row groups; ``w13_scale`` [E, 12, 24, 2, 512]
-    scale atoms; ``w2`` [E, 6144, 384] u8 in checkpoint order; ``w2_scale`` [E, 48, 3, 2, 512] scale atoms."""
+    ``w13`` [E, 12, 24, 17408] u8 and ``w2`` [E, 48, 3, 17408] u8 are streams of tile records: 128 rows x 256
+    K-elements of codes in the 128-byte-swizzled shared-memory image followed by the tile's scale atoms, so a pipeline
+    stage is one contiguous bulk copy. A W13 tile holds 64 gate rows and the matching 64 up rows in 32-row groups.
+    ``w13_scale`` / ``w2_scale`` stay None: the scales travel inside the records."""
     router_weight: torch.Tensor | None
     correction_bias: torch.Tensor | None
     w13: torch.Tensor
-    w13_scale: torch.Tensor
+    w13_scale: torch.Tensor | None
     w2: torch.Tensor
-    w2_scale: torch.Tensor
+    w2_scale: torch.Tensor | None
     routed_scaling_factor: float = 2.0
     routing_mode: str = "sigmoid_bias"
     shared_weights: object | None = None
@@ -91,16 +93,15 @@ class MoeWeights:
         n_exp = w13.shape[0]
         dev = w13.device
         w13, w13_scale, w2, w2_scale = (t.contiguous() for t in (w13, w13_scale, w2, w2_scale))
-        w13p = torch.empty((n_exp, 12, 128, H // 2), dtype=torch.uint8, device=dev)
-        sf13 = torch.empty((n_exp, 12, 24, 2, 512), dtype=torch.uint8, device=dev)
-        sf2 = torch.empty((n_exp, 48, 3, 2, 512), dtype=torch.uint8, device=dev)
+        w13t = torch.empty((n_exp, 12, 24, 17408), dtype=torch.uint8, device=dev)
+        w2t = torch.empty((n_exp, 48, 3, 17408), dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
-            _lib.check(lib.b200moe_preshuffle_w13(_ptr(w13), _ptr(w13_scale), n_exp, _ptr(w13p), _ptr(sf13),
-                                                  _stream(dev)), "preshuffle_w13")
-            _lib.check(lib.b200moe_preshuffle_w2_scales(_ptr(w2_scale), n_exp, _ptr(sf2), _stream(dev)),
-                       "preshuffle_w2_scales")
+            _lib.check(lib.b200moe_preshuffle_w13(_ptr(w13), _ptr(w13_scale), n_exp, _ptr(w13t), _stream(dev)),
+                       "preshuffle_w13")
+            _lib.check(lib.b200moe_preshuffle_w2(_ptr(w2), _ptr(w2_scale), n_exp, _ptr(w2t), _stream(dev)),
+                       "preshuffle_w2")
         bias = None if correction_bias is None else correction_bias.to(device=dev, dtype=torch.float32).contiguous()
-        return cls(router_weight, bias, w13p, sf13, w2, sf2, float(routed_scaling_factor), routing_mode,
+        return cls(router_weight, bias, w13t, None, w2t, None, float(routed_scaling_factor), routing_mode,
                    shared_weights=None, row_major=(w13, w13_scale, w2, w2_scale) if keep_row_major else None)
 
     @property
@@ -110,8 +111,7 @@ class MoeWeights:
     def abi(self) -> _lib.Weights:
         """``struct b200moe_weights`` over this object's tensors."""
         if self._abi is None:
-            self._abi = _lib.Weights(self.w13.data_ptr(), self.w13_scale.data_ptr(), self.w2.data_ptr(),
-                                     self.w2_scale.data_ptr(),
+            self._abi = _lib.Weights(self.w13.data_ptr(), self.w2.data_ptr(),
                                      None if self.correction_bias is None else self.correction_bias.data_ptr(),
                                      self.num_experts, ROUTING_MODES[self.routing_mode],
                                      self.routed_scaling_factor)
@@ -202,16 +202,53 @@ def moe_sort(topk_ids: torch.Tensor, topk_weights: torch.Tensor, bm: int, num_ex
     return buf
 
 
-def dispatch_rows(x_quant, sort: SortBuffers):
-    """Row-major (codes, scales) -> (codes in sorted-row order [rows, 3072], scale atoms [rows/bm, 48, 512])."""
+def dispatch_rows(x_quant, sort: SortBuffers, by_pair: bool = False):
+    """Row-major (codes, scales) -> (codes in sorted-row order [rows, 3072], scale atoms [rows/bm, 48, 512]).
+    ``by_pair``: the input holds one row per (token, slot) pair instead of one per token."""
     codes, scales = x_quant
     dev = codes.device
     xq = torch.empty((sort.max_rows, H // 2), dtype=torch.uint8, device=dev)
     sfx = torch.empty((sort.max_rows // sort.bm, H // 128, 512), dtype=torch.uint8, device=dev)
     _lib.check(_lib.load().b200moe_dispatch_rows(_ptr(codes), _ptr(scales), _ptr(sort.sorted_ids), _ptr(sort.num_valid),
-                                                 sort.tokens, sort.bm, sort.max_rows, _ptr(xq), _ptr(sfx), _stream(dev)),
-               "dispatch_rows")
+                                                 sort.tokens, sort.bm, int(by_pair), sort.max_rows, _ptr(xq), _ptr(sfx),
+                                                 _stream(dev)), "dispatch_rows")
     return xq, sfx
+
+
+def quant_dispatch(x: torch.Tensor, sort: SortBuffers):
+    """bf16 x [M, 6144] -> (codes in sorted-row order, scale atoms): quantisation fused with the gather."""
+    if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expected contiguous BF16 [M,6144]")
+    dev = x.device
+    xq = torch.empty((sort.max_rows, H // 2), dtype=torch.uint8, device=dev)
+    sfx = torch.empty((sort.max_rows // sort.bm, H // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().b200moe_quant_dispatch(_ptr(x), _ptr(sort.sorted_ids), _ptr(sort.num_valid), sort.tokens,
+                                                  sort.bm, sort.max_rows, _ptr(xq), _ptr(sfx), _stream(dev)),
+               "quant_dispatch")
+    return xq, sfx
+
+
+def route_sort(logits: torch.Tensor, w: "MoeWeights", bm: int | None = None):
+    """fp32 logits [M, E] -> (weights, ids, SortBuffers): the router top-4 and the routing sort (one kernel up to 256
+    tokens)."""
+    if logits.dtype != torch.float32 or logits.ndim != 2 or not logits.is_contiguous():
+        raise ValueError("expected contiguous fp32 [M, E] logits")
+    lib = _lib.load()
+    m, n_exp = logits.shape
+    bm = variant_for(m) if bm is None else bm
+    dev = logits.device
+    rows = int(lib.b200moe_max_sorted_rows(m, bm, n_exp))
+    wt = torch.empty((m, TOPK), dtype=torch.float32, device=dev)
+    ids = torch.empty((m, TOPK), dtype=torch.int32, device=dev)
+    buf = SortBuffers(torch.empty(rows, dtype=torch.int32, device=dev), torch.empty(rows, dtype=torch.float32, device=dev),
+                      torch.empty(rows // bm, dtype=torch.int32, device=dev), torch.empty(2, dtype=torch.int32, device=dev),
+                      bm, m)
+    scratch = torch.empty(max(int(lib.b200moe_permute_scratch_bytes(m, n_exp)) // 4, 1), dtype=torch.int32, device=dev)
+    _lib.check(lib.b200moe_route_sort(_ptr(logits), _ptr(w.correction_bias), m, n_exp, ROUTING_MODES[w.routing_mode],
+                                      w.routed_scaling_factor, bm, _ptr(wt), _ptr(ids), _ptr(buf.sorted_ids),
+                                      _ptr(buf.sorted_weights), _ptr(buf.block_expert), _ptr(buf.num_valid),
+                                      _ptr(scratch), _stream(dev)), "route_sort")
+    return wt, ids, buf
 
 
 def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
@@ -219,7 +256,7 @@ def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
     dev = xq_sorted.device
     hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
-    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant(_ptr(w.w13), _ptr(w.w13_scale), w.num_experts, _ptr(xq_sorted),
+    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant(_ptr(w.w13), w.num_experts, _ptr(xq_sorted),
                                                       _ptr(sfx), _ptr(sort.block_expert), _ptr(sort.num_valid),
                                                       sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
                                                       _ptr(status_word(dev)), _stream(dev)), "gemm1_swiglu_quant")
@@ -231,7 +268,7 @@ def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):
     dev = hq.device
     if slots is None:
         slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
-    _lib.check(_lib.load().b200moe_gemm2_weighted(_ptr(w.w2), _ptr(w.w2_scale), w.num_experts, _ptr(hq), _ptr(sfh),
+    _lib.check(_lib.load().b200moe_gemm2_weighted(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
                                                   _ptr(sort.block_expert), _ptr(sort.num_valid), _ptr(sort.sorted_ids),
                                                   _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens,
                                                   _ptr(slots), _ptr(status_word(dev)), _stream(dev)), "gemm2_weighted")

@@ -14,9 +14,11 @@
  *   E8M0 scales: one byte per 32 elements along K, value 2^(byte-127).
  *   "scale atom": 512 bytes holding 4 consecutive scale bytes of up to 128 rows, byte (r%32)*16 + (r/32)*4 + j for row r
  *   and scale j -- the image tcgen05.cp.32x128b.warpx4 moves to tensor memory in one instruction.
- *   Preshuffled W13 [E][12][128][3072]: tile t, row r holds gate (r/32 even) or up (r/32 odd) row
- *   64*t + 32*(r/64) + r%32 of the checkpoint (gate rows 0..767, up rows 768..1535). W2 keeps the checkpoint order.
- *   Weight scales: [E][tiles][K/256][2 atoms], activations scales: [row block][K/128 atoms].
+ *   "tile record": one weight tile of 128 rows x 256 K-elements as 17408 consecutive bytes: 16384 bytes of codes in the
+ *   128-byte-swizzled shared-memory image (row r, 16-byte chunk c at r*128 + ((c ^ (r&7))*16)) followed by the tile's two
+ *   scale atoms. Preshuffled W13 = [E][12 tiles][24 K-tiles] records, tile t row r holding gate (r/32 even) or up (r/32
+ *   odd) row 64*t + 32*(r/64) + r%32 of the checkpoint (gate rows 0..767, up rows 768..1535); preshuffled W2 =
+ *   [E][48 tiles][3 K-tiles] records in checkpoint row order. Activation scales: [row block][K/128 atoms].
  *   Sorted rows: (token, slot) pairs grouped by expert ascending, pair order 4*token+slot inside an expert, every expert
  *   padded to a multiple of bm rows; sorted_ids = token | slot<<24, padding rows carry token = T and weight 0.
  */
@@ -55,11 +57,10 @@ int64_t b200moe_max_sorted_rows(int64_t tokens, int bm, int num_experts);
 int b200moe_block_rows(int64_t tokens);
 
 /* Weight preshuffle, once at load time (MOE/chain.py:41-50 MoeWeights.from_row_major; MOE/layout.py:24-38 w13_layout,
- * w2_layout; MOE/prefill_h6144_i768.py:34-45 Mxfp4PrefillScales.from_row_major). Checkpoint tensors in, kernel layouts
- * out (see "Data formats"); all device pointers; w2 codes need no permutation and are used in place. */
-int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_scale, int num_experts, uint8_t* w13p,
-                           uint8_t* sf13p, void* stream);
-int b200moe_preshuffle_w2_scales(const uint8_t* w2_scale, int num_experts, uint8_t* sf2p, void* stream);
+ * w2_layout; MOE/prefill_h6144_i768.py:34-45 Mxfp4PrefillScales.from_row_major). Checkpoint tensors in, tile records
+ * out (see "Data formats"): w13t [E][12][24][17408], w2t [E][48][3][17408]; all device pointers, 16-byte aligned. */
+int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_scale, int num_experts, uint8_t* w13t, void* stream);
+int b200moe_preshuffle_w2(const uint8_t* w2, const uint8_t* w2_scale, int num_experts, uint8_t* w2t, void* stream);
 
 /* Router top-4 (MOE/router_topk.py:239-272 splitk_biased_topk). logits[t][e] = sum over s<S of
  * partials[t*stride_t + s*stride_s + e], added from 0.0 in split order; plain logits are S=1. mode SIGMOID_BIAS:
@@ -82,29 +83,43 @@ size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
 int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
                     float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
 
+/* Router top-4 on plain fp32 logits [T][num_experts] followed by the routing sort; one single-CTA kernel up to 256
+ * tokens, b200moe_route_topk + b200moe_permute above (the fused top-k + sort of the reference's small tier,
+ * MOE/router_topk_sorted.py:43). Outputs of both. */
+int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, int num_experts, int mode, float scale,
+                       int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids, float* sorted_w,
+                       int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
+
 /* Gather of quantised token rows into sorted order with the scales laid out as atoms (the activation-scale gather of
  * MOE/common/scale_sort_tile_map.py:253 scale_sort_tile_map, plus the row gather the reference does inside GEMM1,
  * MOE/gemm1_prefill_h6144_i768.py:209-228). xq_sorted [max_rows][3072], sfx [max_rows/bm][48][512]; padding rows are
- * written as zero codes with scale byte 127. */
+ * written as zero codes with scale byte 127. by_pair != 0: codes/scales hold one row per (token, slot) pair, row
+ * 4*token+slot (rows that arrived from other ranks), instead of one row per token. */
 int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
-                          const int32_t* num_valid, int64_t tokens, int bm, int64_t max_rows, uint8_t* xq_sorted,
-                          uint8_t* sfx, void* stream);
+                          const int32_t* num_valid, int64_t tokens, int bm, int by_pair, int64_t max_rows,
+                          uint8_t* xq_sorted, uint8_t* sfx, void* stream);
+
+/* Quantisation fused with the gather: bf16 x [T][6144] -> xq_sorted / sfx as above, same bits as b200moe_quant_mxfp4
+ * followed by b200moe_dispatch_rows except that padding rows get the scale byte of an all-zero block (1)
+ * (the fused router + quant launches of the reference, MOE/router_topk_mxfp4_mxfp8_quant.py:35). */
+int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid, int64_t tokens,
+                           int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, void* stream);
 
 /* Grouped GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 block-scaled FP4 MMA
  * (MOE/gemm1_prefill_h6144_i768.py:71-898, MOE/gemm1_a4w4_small.py:75-164; oracle MOE/reference.py:66-72).
  * hq [max_rows][384] codes of h in sorted-row order, sfh [max_rows/bm][6][512] scale atoms. All pointers 16-byte
  * aligned. `status` (device int32) receives B200MOE_DEV_* codes. */
-int b200moe_gemm1_swiglu_quant(const uint8_t* w13p, const uint8_t* sf13p, int num_experts, const uint8_t* xq_sorted,
-                               const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
-                               int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream);
+int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
+                               const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, int bm,
+                               uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream);
 
 /* Grouped GEMM2, times the routing weight, rounded to bf16, one writer per (token, slot, column)
  * (MOE/gemm2_a4w4_small.py:19-79, MOE/gemm2_a4w4_bm128.py:52; oracle MOE/reference.py:73-74).
  * slots bf16 [T][4][6144]; padding rows are dropped. */
-int b200moe_gemm2_weighted(const uint8_t* w2, const uint8_t* sf2p, int num_experts, const uint8_t* hq,
-                           const uint8_t* sfh, const int32_t* block_expert, const int32_t* num_valid,
-                           const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm, int64_t tokens,
-                           void* slots_bf16, int32_t* status, void* stream);
+int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                           const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                           const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
+                           int32_t* status, void* stream);
 
 /* Plain CUDA-core versions of the two grouped GEMMs on checkpoint-layout weights and row-major activations, same
  * outputs and output layouts as the tcgen05 kernels. They exist so the tensor-core kernels and the preshuffle can be
@@ -127,11 +142,9 @@ int b200moe_reduce_slots(const void* slots_bf16, const void* shared_bf16, int64_
  * -> sort -> gather -> GEMM1 -> GEMM2 -> (reduce). `workspace` of b200moe_workspace_bytes(T, num_experts) bytes,
  * 256-byte aligned; out bf16 [T][6144] may be null when only slots [T][4][6144] are wanted (partials mode). */
 typedef struct b200moe_weights {
-  const uint8_t* w13p;
-  const uint8_t* sf13p;
-  const uint8_t* w2;
-  const uint8_t* sf2p;
-  const float* bias; /* may be null */
+  const uint8_t* w13t; /* tile records, b200moe_preshuffle_w13 */
+  const uint8_t* w2t;  /* tile records, b200moe_preshuffle_w2 */
+  const float* bias;   /* may be null */
   int num_experts;
   int route_mode;
   float route_scale;

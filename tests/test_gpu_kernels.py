@@ -165,3 +165,39 @@ def test_reduce_golden_and_shared(C):
     assert np.array_equal(bits_of(out), orc.reduce_slots_bf16(g["slots"], bits_of(shared)))
     with pytest.raises(ValueError):
         C.reduce_slots(slots.float())
+
+
+@pytest.mark.parametrize("m", [1, 3, 64, 256, 257, 3000])
+@pytest.mark.parametrize("mode", ["softmax", "sigmoid_bias"])
+def test_route_sort_equals_route_then_sort(C, m, mode):
+    """The fused single-CTA kernel (<= 256 tokens) and the split launches give the oracle's routing and permutation."""
+    from types import SimpleNamespace
+    rng = np.random.default_rng(m)
+    lg = rng.standard_normal((m, 128)).astype(np.float32)
+    bias = (rng.standard_normal(128) * 0.05).astype(np.float32)
+    scale = 1.0 if mode == "softmax" else 2.0
+    w = SimpleNamespace(correction_bias=dev(bias), routing_mode=mode, routed_scaling_factor=scale)
+    wt, ids, sb = C.route_sort(dev(lg), w)
+    wt2, ids2 = C.topk_route(dev(lg), dev(bias), scale, mode)
+    assert torch.equal(ids, ids2) and torch.equal(wt, wt2)
+    rows, wts, blocks, nv = orc.permute(ids.cpu().numpy(), wt.cpu().numpy(), sb.bm)
+    assert np.array_equal(sb.num_valid.cpu().numpy(), nv)
+    assert np.array_equal(sb.sorted_ids.cpu().numpy()[:nv[0]], rows)
+    assert np.array_equal(sb.sorted_weights.cpu().numpy()[:nv[0]].view(np.uint32), wts.view(np.uint32))
+    assert np.array_equal(sb.block_expert.cpu().numpy()[:nv[0] // sb.bm], blocks)
+
+
+@pytest.mark.parametrize("m,bm", [(2, 16), (50, 32), (130, 64), (700, 128)])
+def test_quant_dispatch_equals_quant_then_gather(C, m, bm):
+    gen = torch.Generator().manual_seed(m)
+    x = torch.randn((m, 192, 32), generator=gen) * torch.exp2(torch.randint(-10, 11, (m, 192, 1), generator=gen).float())
+    x = x.view(m, 6144).bfloat16().cuda()
+    ids, w = make_routing(m, "hot", seed=m)
+    sb = C.moe_sort(dev(ids), dev(w), bm)
+    a_codes, a_sf = C.quant_dispatch(x, sb)
+    b_codes, b_sf = C.dispatch_rows(C.mxfp4_quant(x), sb)
+    nv = int(sb.num_valid[0])
+    live = ((sb.sorted_ids[:nv] & 0xFFFFFF) < m).cpu().numpy()
+    assert torch.equal(a_codes[:nv], b_codes[:nv])
+    sa, sr = (atoms_to_rowmajor(t.cpu().numpy(), bm)[:nv] for t in (a_sf, b_sf))
+    assert np.array_equal(sa[live], sr[live]) and np.all(sa[~live] == 1)
