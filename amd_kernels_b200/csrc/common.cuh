@@ -26,6 +26,57 @@ constexpr int kTileRecordBytes = 128 * 128 + 2 * kAtomBytes;  // one weight tile
     if (e__ != cudaSuccess) return static_cast<int>(e__); \
   } while (0)
 
+// Programmatic dependent launch: every kernel of the library is launched with the programmatic-serialization attribute,
+// lets its successor start early (launch_dependents) and waits for its predecessors' memory (wait) before it touches
+// global memory. A successor therefore overlaps its launch latency and set-up with the tail of the kernel before it.
+//
+// Two rules follow from a kernel being resident BEFORE its inputs exist: (1) pointers to data a predecessor writes are
+// laundered through an empty asm after the wait, so the compiler cannot hoist a load (const __restrict__ loads count as
+// invariant and would otherwise move above the wait); (2) such data is read with L2-coherent loads (ld.global.cg, TMA or
+// bulk copies), never through the non-coherent L1 path, which may hold lines an older kernel fetched on the same SM.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename T>
+__device__ __forceinline__ void launder(T& p) {  // T is a (possibly __restrict__) pointer type
+  asm volatile("" : "+l"(p)::"memory");
+}
+// launch the successor early, wait for the predecessors, then forget everything known about the given pointers
+template <typename... P>
+__device__ __forceinline__ void pdl_enter(P&... ptrs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  (launder(ptrs), ...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// kernels outside the per-call chain (load-time preshuffle, cross-check kernels) use ordinary stream order
+#define B200MOE_LAUNCH_PLAIN(kernel, grid, block, smem, stream, ...)          \
+  do {                                                                        \
+    kernel<<<grid, block, smem, stream>>>(__VA_ARGS__);                       \
+    B200MOE_CHECK_LAUNCH();                                                   \
+  } while (0)
+
+#define B200MOE_LAUNCH(kernel, grid, block, smem, stream, ...)                                        \
+  do {                                                                                                \
+    cudaError_t e__ = b200moe::launch_pdl(kernel, grid, block, smem, stream, __VA_ARGS__);            \
+    if (e__ != cudaSuccess) return static_cast<int>(e__);                                             \
+  } while (0)
+
 __device__ __forceinline__ float e2m1_value(uint32_t code) {
   // {0,.5,1,1.5,2,3,4,6} with the sign in bit 3
   const uint32_t m = code & 7u;

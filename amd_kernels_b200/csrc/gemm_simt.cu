@@ -131,9 +131,7 @@ extern "C" int b200moe_gemm1_simt(const uint8_t* w13, const uint8_t* w13_scale, 
   if (bm != 16 && bm != 32 && bm != 64 && bm != 128) return B200MOE_E_ARG;
   const int64_t n = rows ? n_rows : max_rows;
   if (n <= 0) return 0;
-  gemm1_simt_kernel<<<dim3(static_cast<unsigned>(n), kI / 32), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      w13, w13_scale, codes, scales, sorted_ids, block_expert, num_valid, rows, bm, tokens, hq, sfh);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN(gemm1_simt_kernel, dim3(static_cast<unsigned>(n), kI / 32), 256, 0, static_cast<cudaStream_t>(stream), w13, w13_scale, codes, scales, sorted_ids, block_expert, num_valid, rows, bm, tokens, hq, sfh);
   return 0;
 }
 
@@ -147,9 +145,6 @@ extern "C" int b200moe_gemm2_simt(const uint8_t* w2, const uint8_t* w2_scale, co
   if (bm != 16 && bm != 32 && bm != 64 && bm != 128) return B200MOE_E_ARG;
   const int64_t n = rows ? n_rows : max_rows;
   if (n <= 0) return 0;
-  gemm2_simt_kernel<<<dim3(static_cast<unsigned>(n), kH / 64), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      w2, w2_scale, hq, sfh, sorted_ids, sorted_w, block_expert, num_valid, rows, bm, tokens,
-      static_cast<__nv_bfloat16*>(slots_bf16));
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN(gemm2_simt_kernel, dim3(static_cast<unsigned>(n), kH / 64), 256, 0, static_cast<cudaStream_t>(stream), w2, w2_scale, hq, sfh, sorted_ids, sorted_w, block_expert, num_valid, rows, bm, tokens, static_cast<__nv_bfloat16*>(slots_bf16));
   return 0;
 }

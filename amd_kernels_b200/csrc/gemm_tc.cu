@@ -137,7 +137,7 @@ struct Cfg {
   static constexpr int kBOffset = kTileRecordBytes;
   static constexpr int kSfbOffset = kBOffset + kBBytes;
   static constexpr int kStageBytes = kSfbOffset + kSfBytes;
-  static constexpr int kStages = MODE == 1 ? (BM == 128 ? 5 : (BM == 64 ? 6 : 8)) : (BM == 128 ? 6 : 8);
+  static constexpr int kStages = MODE == 1 ? (BM == 128 ? 5 : (BM == 64 ? 6 : 8)) : (BM == 128 ? 5 : 8);
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   static constexpr int kSfaCol = 2 * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
@@ -146,7 +146,10 @@ struct Cfg {
   // GEMM1 epilogue staging: up to 64 token columns x (2 groups x (32 gate + 32 up + 4 pad)) floats
   static constexpr int kEpiCols = BM < 64 ? BM : 64;
   static constexpr int kEpiRowFloats = 136;
-  static constexpr int kEpiBytes = MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : 0;
+  // GEMM2 epilogue staging: up to 32 token columns x (128 output columns + 4 pad) floats
+  static constexpr int kOutCols = BM < 32 ? BM : 32;
+  static constexpr int kOutRowFloats = 132;
+  static constexpr int kEpiBytes = MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : kOutCols * kOutRowFloats * 4;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;  // + slack to align to 1024 bytes
   static constexpr int kActAtomsPerBlock = MODE == 1 ? kH / 128 : kI / 128;  // activation scale atoms per row block
   static constexpr int kActRowBytes = MODE == 1 ? kH / 2 : kI / 2;
@@ -176,7 +179,8 @@ template <int MODE, int BM>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                         const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
-                        const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status) {
+                        const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status, int num_experts,
+                        int max_blocks) {
   using C = Cfg<MODE, BM>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
@@ -185,10 +189,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int s_sid[MODE == 2 ? BM : 1];
+  __shared__ float s_wt[MODE == 2 ? BM : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   volatile int* abort_v = &abort_flag;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -214,7 +221,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  const int n_blocks = num_valid[0] / BM;
+  // barriers and TMEM are set up; from here on the kernel reads what its predecessors wrote
+  pdl_wait();
+  launder(w_tiles);
+  launder(sf_x);
+  launder(block_expert);
+  launder(num_valid);
+  launder(ep.sorted_ids);
+  launder(ep.sorted_w);
+  int n_blocks = __ldcg(num_valid) / BM;
+  if (n_blocks < 0 || n_blocks > max_blocks) {  // a routing table that does not fit its buffers: record it, do nothing
+    if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
+    n_blocks = 0;
+  }
   const int total_units = n_blocks * C::kTilesM;
 
   if (warp == 0) {
@@ -224,7 +243,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const int b = u / C::kTilesM, mt = u % C::kTilesM;
-        const int e = block_expert[b];
+        int e = __ldcg(block_expert + b);
+        if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
+          atomicExch(status, B200MOE_DEV_BAD_INDEX);
+          e = 0;
+        }
         const uint8_t* w_src = w_tiles + static_cast<int64_t>(e * C::kTilesM + mt) * C::kTilesK * kTileRecordBytes;
         const uint8_t* sfb_src = sf_x + static_cast<int64_t>(b) * C::kActAtomsPerBlock * kAtomBytes;
         for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
@@ -293,15 +316,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
-      int sid[(BM + 31) / 32];
-      float wt[(BM + 31) / 32];
-      if (MODE == 2) {
-#pragma unroll
-        for (int r = 0; r < (BM + 31) / 32; ++r) {
-          const int row = r * 32 + lane;
-          sid[r] = row < BM ? __ldg(ep.sorted_ids + row0 + row) : 0x00ffffff;
-          wt[r] = row < BM ? __ldg(ep.sorted_w + row0 + row) : 0.0f;
-        }
+      if (MODE == 2 && et < BM) {  // this block's rows: fetched before the wait so the latency hides behind the MMAs
+        s_sid[et] = __ldcg(ep.sorted_ids + row0 + et);
+        s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
       }
       // the four warps must agree before they meet at the named barrier below
       if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status))) break;
@@ -362,23 +379,40 @@ __global__ void __launch_bounds__(kThreads, 1)
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       } else {
+        // Stage the accumulators as [token][128 columns] so a warp writes one token's 128 columns as 256 contiguous bytes.
+        float* mine = stage_f + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BM; c0 += C::kOutCols) {
 #pragma unroll
-        for (int c = 0; c < BM / 16; ++c) {
-          uint32_t v[16];
-          tc_ld16(t_acc + c * 16, v);
+          for (int cc = 0; cc < C::kOutCols; cc += 16) {
+            uint32_t v[16];
+            tc_ld16(t_acc + c0 + cc, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int col = c * 16 + j;
-            const int s_id = __shfl_sync(0xffffffffu, sid[col >> 5], col & 31);
-            const float s_w = __shfl_sync(0xffffffffu, wt[col >> 5], col & 31);
-            const int64_t token = s_id & 0x00ffffff;
-            if (token < ep.tokens)
-              ep.slots[(token * kTopK + (s_id >> 24)) * kH + mt * 128 + q * 32 + lane] =
-                  __float2bfloat16_rn(__uint_as_float(v[j]) * s_w);
+            for (int j = 0; j < 16; ++j) mine[(cc + j) * C::kOutRowFloats] = __uint_as_float(v[j]);
           }
+          if (c0 + C::kOutCols >= BM) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 2
+          for (int item = et; item < C::kOutCols * 32; item += 128) {
+            const int j = item >> 5, seg = item & 31;
+            const int s_id = s_sid[c0 + j];
+            const int64_t token = s_id & 0x00ffffff;
+            if (token < ep.tokens) {
+              const float s_w = s_wt[c0 + j];
+              const float4 v = *reinterpret_cast<const float4*>(stage_f + j * C::kOutRowFloats + seg * 4);
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * s_w, v.y * s_w);
+              const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * s_w, v.w * s_w);
+              uint2 packed;
+              packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+              packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(ep.slots + (token * kTopK + ((s_id >> 24) & 3)) * kH + mt * 128 + seg * 4) = packed;
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bar_tempty[acc]));
       }
     }
   }
@@ -437,7 +471,7 @@ static int sm_count() {
 template <int MODE, int BM>
 static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
-                  int32_t* status, cudaStream_t stream) {
+                  int num_experts, int32_t* status, cudaStream_t stream) {
   using C = Cfg<MODE, BM>;
   static bool configured = false;
   if (!configured) {
@@ -449,21 +483,19 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
   const int64_t max_units = max_rows / BM * C::kTilesM;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   if (grid <= 0) return 0;
-  grouped_gemm_kernel<MODE, BM><<<grid, kThreads, C::kSmemBytes, stream>>>(mx, w_tiles, sf_x, block_expert, num_valid, ep,
-                                                                          status);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
 
 template <int MODE>
 static int launch_bm(int bm, const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                      const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
-                     int32_t* status, cudaStream_t stream) {
+                     int num_experts, int32_t* status, cudaStream_t stream) {
   switch (bm) {
-    case 16: return launch<MODE, 16>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 32: return launch<MODE, 32>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 64: return launch<MODE, 64>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
-    case 128: return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, status, stream);
+    case 16: return launch<MODE, 16>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
+    case 32: return launch<MODE, 32>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
+    case 64: return launch<MODE, 64>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
+    case 128: return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
   }
   return B200MOE_E_ARG;
 }
@@ -491,7 +523,7 @@ extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, 
   EpilogueArgs ep{};
   ep.hq = hq;
   ep.sfh = sfh;
-  return launch_bm<1>(bm, mx, w13t, sfx, block_expert, num_valid, ep, max_rows, status,
+  return launch_bm<1>(bm, mx, w13t, sfx, block_expert, num_valid, ep, max_rows, num_experts, status,
                       static_cast<cudaStream_t>(stream));
 }
 
@@ -515,6 +547,6 @@ extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const
   ep.sorted_w = sorted_w;
   ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
   ep.tokens = tokens;
-  return launch_bm<2>(bm, mx, w2t, sfh, block_expert, num_valid, ep, max_rows, status,
+  return launch_bm<2>(bm, mx, w2t, sfh, block_expert, num_valid, ep, max_rows, num_experts, status,
                       static_cast<cudaStream_t>(stream));
 }

@@ -46,9 +46,7 @@ extern "C" int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_sca
   using namespace b200moe;
   if (!w13 || !w13_scale || !w13t || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w13) & 15) || (reinterpret_cast<uintptr_t>(w13t) & 15)) return B200MOE_E_ALIGN;
-  preshuffle_kernel<kH / 2, kW13Tiles, true>
-      <<<dim3(128, kW13Tiles, num_experts), 192, 0, static_cast<cudaStream_t>(stream)>>>(w13, w13_scale, w13t);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kH / 2, kW13Tiles, true>), dim3(128, kW13Tiles, num_experts), 192, 0, static_cast<cudaStream_t>(stream), w13, w13_scale, w13t);
   return 0;
 }
 
@@ -57,8 +55,6 @@ extern "C" int b200moe_preshuffle_w2(const uint8_t* w2, const uint8_t* w2_scale,
   using namespace b200moe;
   if (!w2 || !w2_scale || !w2t || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w2) & 15) || (reinterpret_cast<uintptr_t>(w2t) & 15)) return B200MOE_E_ALIGN;
-  preshuffle_kernel<kI / 2, kW2Tiles, false>
-      <<<dim3(128, kW2Tiles, num_experts), 32, 0, static_cast<cudaStream_t>(stream)>>>(w2, w2_scale, w2t);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kI / 2, kW2Tiles, false>), dim3(128, kW2Tiles, num_experts), 32, 0, static_cast<cudaStream_t>(stream), w2, w2_scale, w2t);
   return 0;
 }

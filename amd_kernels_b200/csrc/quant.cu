@@ -67,10 +67,11 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
                                                              const int32_t* __restrict__ num_valid, int64_t tokens,
                                                              int bm_shift, uint8_t* __restrict__ xq_sorted,
                                                              uint8_t* __restrict__ sfx) {
+  pdl_enter(x, sorted_ids, num_valid);
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= num_valid[0]) return;
-  const int64_t token = sorted_ids[row] & 0x00ffffff;
+  if (row >= __ldcg(num_valid)) return;
+  const int64_t token = __ldcg(sorted_ids + row) & 0x00ffffff;
   const bool pad = token >= tokens;
   const uint4* src = x + token * (kH / 8);
   uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + row * (kH / 2));
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
 #pragma unroll 4
   for (int it = 0; it < kH / 8 / 32; ++it) {
     const int idx = it * 32 + lane;
-    const uint4 raw = pad ? make_uint4(0, 0, 0, 0) : src[idx];
+    const uint4 raw = pad ? make_uint4(0, 0, 0, 0) : __ldcg(src + idx);
     const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
     float v[8];
 #pragma unroll
@@ -115,9 +116,7 @@ extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, ui
   if (tokens == 0) return 0;
   const int64_t n_vec = tokens * (k / 8);
   const unsigned grid = static_cast<unsigned>((n_vec + 255) / 256);
-  quant_mxfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x_bf16), n_vec, k, reinterpret_cast<uint32_t*>(codes), scales);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN(quant_mxfp4_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), n_vec, k, reinterpret_cast<uint32_t*>(codes), scales);
   return 0;
 }
 
@@ -133,9 +132,7 @@ extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
   const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
-  dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, scales, sorted_ids, num_valid,
-                                                                            tokens, bm, by_pair, xq_sorted, sfx);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH_PLAIN(dispatch_rows_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), codes, scales, sorted_ids, num_valid, tokens, bm, by_pair, xq_sorted, sfx);
   return 0;
 }
 
@@ -151,8 +148,6 @@ extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
   const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
-  quant_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH(quant_dispatch_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx);
   return 0;
 }

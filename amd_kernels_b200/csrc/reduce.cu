@@ -15,6 +15,7 @@ __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4 v) {
 __global__ void __launch_bounds__(256) reduce_slots_kernel(const uint4* __restrict__ slots,
                                                            const uint4* __restrict__ shared, int64_t n_vec,
                                                            uint4* __restrict__ out) {
+  pdl_enter(slots, shared);
   constexpr int kVecPerRow = kH / 8;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_vec) return;
@@ -23,8 +24,8 @@ __global__ void __launch_bounds__(256) reduce_slots_kernel(const uint4* __restri
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
 #pragma unroll
-  for (int s = 0; s < kTopK; ++s) add_bf16x8(acc, slots[(t * kTopK + s) * kVecPerRow + c]);
-  if (shared) add_bf16x8(acc, shared[i]);
+  for (int s = 0; s < kTopK; ++s) add_bf16x8(acc, __ldcg(slots + (t * kTopK + s) * kVecPerRow + c));
+  if (shared) add_bf16x8(acc, __ldcg(shared + i));
   uint32_t o[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -45,9 +46,6 @@ extern "C" int b200moe_reduce_slots(const void* slots_bf16, const void* shared_b
     return B200MOE_E_ALIGN;
   if (tokens == 0) return 0;
   const int64_t n_vec = tokens * (kH / 8);
-  reduce_slots_kernel<<<static_cast<unsigned>((n_vec + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(slots_bf16), static_cast<const uint4*>(shared_bf16), n_vec,
-      static_cast<uint4*>(out_bf16));
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH(reduce_slots_kernel, static_cast<unsigned>((n_vec + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(slots_bf16), static_cast<const uint4*>(shared_bf16), n_vec, static_cast<uint4*>(out_bf16));
   return 0;
 }

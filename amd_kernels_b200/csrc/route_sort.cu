@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
                                                          int64_t stride_s, int splits, const float* __restrict__ bias,
                                                          int64_t tokens, int num_experts, float scale,
                                                          float* __restrict__ out_w, int32_t* __restrict__ out_ids) {
+  pdl_enter(partials, bias);
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
@@ -98,12 +99,13 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
 
 __global__ void __launch_bounds__(kChunk) permute_count_kernel(const int32_t* __restrict__ ids, int64_t pairs,
                                                                int num_experts, int32_t* __restrict__ cta_counts) {
+  pdl_enter(ids);
   __shared__ int hist[kMaxE];
   if (threadIdx.x < kMaxE) hist[threadIdx.x] = 0;
   __syncthreads();
   const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
   if (q < pairs) {
-    const int e = ids[q];
+    const int e = __ldcg(ids + q);
     if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
   }
   __syncthreads();
@@ -149,7 +151,7 @@ __device__ __forceinline__ void place_chunk(SortShared& sh, int e, float wv, int
     if (cta_counts != nullptr) {
       t = 0;
       for (unsigned c = 0; c < gridDim.x; ++c) {
-        const int n = cta_counts[static_cast<int64_t>(c) * num_experts + tid];
+        const int n = __ldcg(cta_counts + static_cast<int64_t>(c) * num_experts + tid);
         if (c < blockIdx.x) b += n;
         t += n;
       }
@@ -219,14 +221,15 @@ __global__ void __launch_bounds__(kChunk) permute_place_kernel(const int32_t* __
                                                                float* __restrict__ sorted_w,
                                                                int32_t* __restrict__ block_expert,
                                                                int32_t* __restrict__ num_valid) {
+  pdl_enter(ids, w, cta_counts);
   __shared__ SortShared sh;
   const int64_t pairs = tokens * kTopK;
   const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
   int e = -1;
   float wv = 0.0f;
   if (q < pairs) {
-    e = ids[q];
-    wv = w[q];
+    e = __ldcg(ids + q);
+    wv = __ldcg(w + q);
     if (e < 0 || e >= num_experts) e = -1;
   }
   place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, cta_counts, sorted_ids, sorted_w, block_expert, num_valid);
@@ -242,6 +245,7 @@ __global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restr
                                                             float* __restrict__ sorted_w,
                                                             int32_t* __restrict__ block_expert,
                                                             int32_t* __restrict__ num_valid) {
+  pdl_enter(logits, bias);
   __shared__ SortShared sh;
   __shared__ int s_ids[kChunk];
   __shared__ float s_w[kChunk];
@@ -286,12 +290,11 @@ extern "C" int b200moe_route_topk(const float* partials, int64_t stride_t, int64
   const unsigned grid = static_cast<unsigned>((tokens + warps - 1) / warps);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (mode == B200MOE_ROUTE_SIGMOID_BIAS)
-    route_topk_kernel<B200MOE_ROUTE_SIGMOID_BIAS><<<grid, warps * 32, 0, s>>>(partials, stride_t, stride_s, splits, bias,
-                                                                             tokens, num_experts, scale, out_w, out_ids);
+    B200MOE_LAUNCH((route_topk_kernel<B200MOE_ROUTE_SIGMOID_BIAS>), grid, warps * 32, 0, s, partials, stride_t, stride_s,
+                   splits, bias, tokens, num_experts, scale, out_w, out_ids);
   else
-    route_topk_kernel<B200MOE_ROUTE_SOFTMAX><<<grid, warps * 32, 0, s>>>(partials, stride_t, stride_s, splits, bias,
-                                                                        tokens, num_experts, scale, out_w, out_ids);
-  B200MOE_CHECK_LAUNCH();
+    B200MOE_LAUNCH((route_topk_kernel<B200MOE_ROUTE_SOFTMAX>), grid, warps * 32, 0, s, partials, stride_t, stride_s, splits,
+                   bias, tokens, num_experts, scale, out_w, out_ids);
   return 0;
 }
 
@@ -326,12 +329,9 @@ extern "C" int b200moe_permute(const int32_t* ids, const float* w, int64_t token
   if (chunks > 1 && !scratch) return B200MOE_E_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (chunks > 1) {
-    permute_count_kernel<<<chunks, kChunk, 0, s>>>(ids, pairs, num_experts, scratch);
-    B200MOE_CHECK_LAUNCH();
+    B200MOE_LAUNCH(permute_count_kernel, chunks, kChunk, 0, s, ids, pairs, num_experts, scratch);
   }
-  permute_place_kernel<<<chunks, kChunk, 0, s>>>(ids, w, tokens, num_experts, shift, chunks > 1 ? scratch : nullptr,
-                                                 sorted_ids, sorted_w, block_expert, num_valid);
-  B200MOE_CHECK_LAUNCH();
+  B200MOE_LAUNCH(permute_place_kernel, chunks, kChunk, 0, s, ids, w, tokens, num_experts, shift, chunks > 1 ? scratch : nullptr, sorted_ids, sorted_w, block_expert, num_valid);
   return 0;
 }
 
@@ -353,13 +353,10 @@ extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (mode == B200MOE_ROUTE_SIGMOID_BIAS)
-    route_sort_kernel<B200MOE_ROUTE_SIGMOID_BIAS><<<1, kChunk, 0, s>>>(logits, bias, static_cast<int>(tokens), num_experts,
-                                                                      scale, shift, out_w, out_ids, sorted_ids, sorted_w,
-                                                                      block_expert, num_valid);
+    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SIGMOID_BIAS>), 1, kChunk, 0, s, logits, bias, static_cast<int>(tokens),
+                   num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, num_valid);
   else
-    route_sort_kernel<B200MOE_ROUTE_SOFTMAX><<<1, kChunk, 0, s>>>(logits, bias, static_cast<int>(tokens), num_experts,
-                                                                 scale, shift, out_w, out_ids, sorted_ids, sorted_w,
-                                                                 block_expert, num_valid);
-  B200MOE_CHECK_LAUNCH();
+    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SOFTMAX>), 1, kChunk, 0, s, logits, bias, static_cast<int>(tokens),
+                   num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, num_valid);
   return 0;
 }

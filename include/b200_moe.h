@@ -42,6 +42,7 @@ extern "C" {
 #define B200MOE_E_ALIGN (-2)   /* a pointer that must be 16-byte (workspace: 256-byte) aligned is not */
 #define B200MOE_E_DRIVER (-3)  /* the CUDA driver entry point for tensor maps is unavailable */
 #define B200MOE_DEV_TIMEOUT 1  /* a bounded mbarrier wait ran out inside a kernel */
+#define B200MOE_DEV_BAD_INDEX 2 /* a block count or expert id read from the routing table was out of range */
 
 #define B200MOE_ROUTE_SIGMOID_BIAS 0 /* the reference's rule */
 #define B200MOE_ROUTE_SOFTMAX 1      /* softmax, top-4, renormalised over the picks */
