@@ -104,6 +104,14 @@ __device__ __forceinline__ uint32_t e2m1_code(float v, int e) {
   return c | ((__float_as_uint(v) >> 31) << 3);
 }
 
+// two E2M1 codes in one byte: `lo` in the low nibble, `hi` in the high nibble; round to nearest even, saturating.
+// Same codes as e2m1_code on a value already divided by the block scale (ties go to the even code, -0 keeps its sign).
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+  uint16_t out;
+  asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u16.u8 %0, t;\n}\n" : "=h"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+
 __device__ __forceinline__ float swiglu_oai(float g, float u) {
   g = fminf(g, 7.0f);
   u = fminf(fmaxf(u, -7.0f), 7.0f);

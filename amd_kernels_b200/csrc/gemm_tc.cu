@@ -168,13 +168,6 @@ struct EpilogueArgs {
 
 constexpr int kThreads = 192;
 
-// two E2M1 codes in one byte: `lo` in the low nibble, `hi` in the high nibble; round to nearest even, saturating
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
-  uint16_t out;
-  asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u16.u8 %0, t;\n}\n" : "=h"(out) : "f"(hi), "f"(lo));
-  return out;
-}
-
 template <int MODE, int BM>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,

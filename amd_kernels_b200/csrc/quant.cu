@@ -77,10 +77,18 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
   uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + row * (kH / 2));
   const int r = static_cast<int>(row & ((1 << bm_shift) - 1));
   uint8_t* sdst = sfx + (row >> bm_shift) * (kH / 128) * kAtomBytes + atom_offset(r, 0);
+  if (pad) {  // a padding row: zero codes, the scale byte of an all-zero block
+#pragma unroll 4
+    for (int it = 0; it < kH / 8 / 32; ++it) {
+      dst[it * 32 + lane] = 0u;
+      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (it * 2 + (lane >> 4)) * kAtomBytes) = 0x01010101u;
+    }
+    return;
+  }
 #pragma unroll 4
   for (int it = 0; it < kH / 8 / 32; ++it) {
     const int idx = it * 32 + lane;
-    const uint4 raw = pad ? make_uint4(0, 0, 0, 0) : __ldcg(src + idx);
+    const uint4 raw = __ldcg(src + idx);
     const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
     float v[8];
 #pragma unroll
@@ -94,9 +102,10 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const int e = quark_even_e8m0(amax);
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);  // 2^(127-e), exact
     uint32_t packed = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) packed |= e2m1_code(v[j], e) << (4 * j);
+    for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
     dst[idx] = packed;
     // 8 blocks of 32 per warp step = 2 atoms' worth of 4 scale bytes: lanes 0 and 16 gather 4 neighbours' bytes
     uint32_t sc = static_cast<uint32_t>(e);

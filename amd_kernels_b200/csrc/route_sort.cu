@@ -9,6 +9,7 @@
 namespace b200moe {
 
 constexpr int kChunk = 1024;
+constexpr int kFusedRouteTokens = 32;  // up to here the single-CTA kernel routes one token per warp and sorts
 
 // (value, id) ordering: larger value first, equal values to the lower id.
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
@@ -345,7 +346,7 @@ extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_
   if (mode != B200MOE_ROUTE_SIGMOID_BIAS && mode != B200MOE_ROUTE_SOFTMAX) return B200MOE_E_ARG;
   const int shift = shift_of(bm);
   if (shift < 0) return B200MOE_E_ARG;
-  if (tokens * kTopK > kChunk) {
+  if (tokens > kFusedRouteTokens) {  // many tokens: route on many SMs first, then sort
     int r = b200moe_route_topk(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, out_w, out_ids, stream);
     if (r) return r;
     return b200moe_permute(out_ids, out_w, tokens, num_experts, bm, sorted_ids, sorted_w, block_expert, num_valid, scratch,

@@ -1,0 +1,139 @@
+"""Expert-parallel form of the routed MXFP4 MoE layer: the 128 experts are sharded over W ranks (one process per GPU),
+every rank routes its own tokens, sends each (token, slot) pair's quantised row to the rank that owns the expert
+(all-to-all over NCCL), runs the grouped GEMMs on the rows it received and returns the bf16 slot rows (second
+all-to-all); the source rank sums a token's four slots in slot order.
+
+The reference has no expert parallelism (its multi-GPU form is tensor parallel with a sequence-parallel gather,
+amd_kernels/moe/mxfp4_h6144_i768_e128_top4/prepared_input.py:116-209); what carries over is its idea of shipping the
+quantised activations (3264 bytes per row) instead of bf16 (12288 bytes), and its fixed-order combine
+(amd_kernels/collectives/pull_collectives_ranks4/reference.py:74-91). Because a (token, slot) row is one accumulator
+column of the grouped GEMMs whatever else is in the batch, and the combine adds slots 0..3 in order, the result is
+bit-identical to the single-GPU layer for every W.
+
+The exchange bookkeeping (``plan_dispatch`` / ``scatter_combined``) is plain index arithmetic on torch tensors and runs
+on CPU tensors too, which is how the world_size-2 gloo tests exercise it without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+H, I, E, TOPK = 6144, 768, 128, 4  # noqa: E741
+
+
+def expert_owner(ids: torch.Tensor, world: int, experts: int = E, placement: str = "contiguous"):
+    """(owning rank, expert id local to that rank) of global expert ids. "contiguous": rank r owns experts
+    [r*E/W, (r+1)*E/W); "interleaved": expert e lives on rank e % W (spreads a popularity ranking that follows the id)."""
+    per = experts // world
+    if placement == "contiguous":
+        return ids // per, ids % per
+    if placement == "interleaved":
+        return ids % world, ids // world
+    raise ValueError("placement must be 'contiguous' or 'interleaved'")
+
+
+def local_expert_ids(rank: int, world: int, experts: int = E, placement: str = "contiguous") -> torch.Tensor:
+    """Global ids of the experts rank ``rank`` owns, in local-id order."""
+    per = experts // world
+    if placement == "contiguous":
+        return torch.arange(rank * per, (rank + 1) * per)
+    return torch.arange(per) * world + rank
+
+
+@dataclass
+class DispatchPlan:
+    order: torch.Tensor        # int64 [4T]: pair index q = 4*token+slot of each sent row, grouped by destination rank
+    send_counts: list          # rows per destination rank
+    local_expert: torch.Tensor  # int32 [4T]: the expert id on the destination rank, in send order
+    weight: torch.Tensor       # fp32 [4T]: the routing weight, in send order
+
+
+def plan_dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, world: int, experts: int = E,
+                  placement: str = "contiguous") -> DispatchPlan:
+    """Group the 4T pairs by destination rank, keeping pair order inside a destination."""
+    dest, local = expert_owner(topk_ids.reshape(-1).long(), world, experts, placement)
+    order = torch.argsort(dest, stable=True)
+    counts = torch.bincount(dest, minlength=world)
+    return DispatchPlan(order, counts.tolist(), local[order].int(), topk_weights.reshape(-1)[order].float())
+
+
+def exchange_counts(send_counts, group) -> list:
+    """All-to-all of the per-destination row counts -> rows arriving from every source rank."""
+    device = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    send = torch.tensor(send_counts, dtype=torch.int64, device=device)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.tolist()
+
+
+def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
+    """Variable-size all-to-all of whole rows (dim 0)."""
+    out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
+                           input_split_sizes=list(send_counts), group=group)
+    return out
+
+
+def scatter_combined(returned: torch.Tensor, plan: DispatchPlan, tokens: int) -> torch.Tensor:
+    """Rows that came back in send order -> slots [T, 4, width] (row q = 4*token+slot)."""
+    slots = returned.new_empty((tokens * TOPK,) + tuple(returned.shape[1:]))
+    slots[plan.order] = returned
+    return slots.view(tokens, TOPK, *returned.shape[1:])
+
+
+class ExpertParallelMoe:
+    """One rank of the expert-parallel layer. ``weights`` holds this rank's experts only
+    (``MoeWeights.from_row_major`` on the slice ``local_expert_ids(rank, world)`` of the checkpoint); routing parameters
+    (bias over all 128 experts, mode, scale) describe the global router."""
+
+    def __init__(self, weights, group=None, *, bias=None, routing_mode="softmax", scale=1.0, placement="contiguous",
+                 experts: int = E):
+        self.w, self.group = weights, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if experts % self.world or weights.num_experts != experts // self.world:
+            raise ValueError(f"needs {experts // self.world} local experts on each of {self.world} ranks")
+        self.bias, self.mode, self.scale, self.placement, self.experts = bias, routing_mode, float(scale), placement, experts
+        self.last_recv_rows = 0
+
+    def experts_on_rows(self, codes, scales, local_expert, weight):
+        """The grouped GEMMs on rows that arrived from any rank: row r -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r."""
+        from . import chain
+        n = codes.shape[0]
+        if n == 0:
+            return torch.empty((0, H), dtype=torch.bfloat16, device=codes.device)
+        groups = (n + TOPK - 1) // TOPK  # rows are handed to the sort as pseudo-tokens of four pairs
+        pad = groups * TOPK - n
+        if pad:
+            local_expert = torch.cat([local_expert, local_expert.new_full((pad,), -1)])  # ids outside the range are dropped
+            weight = torch.cat([weight, weight.new_zeros(pad)])
+            codes = torch.cat([codes, codes.new_zeros((pad, codes.shape[1]))])
+            scales = torch.cat([scales, scales.new_zeros((pad, scales.shape[1]))])
+        bm = chain.variant_for(groups)
+        sort = chain.moe_sort(local_expert.view(groups, TOPK).contiguous(), weight.view(groups, TOPK).contiguous(), bm,
+                              self.w.num_experts)
+        xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
+        hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
+        slots = chain.grouped_gemm2(hq, sfh, sort, self.w)
+        return slots.view(groups * TOPK, H)[:n]
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor, *, return_partials=False):
+        """x bf16 [T_local, 6144], fp32 logits [T_local, 128] -> bf16 [T_local, 6144] (or the slots [T_local, 4, 6144])."""
+        from . import chain
+        tokens = x.shape[0]
+        chain.variant_for(tokens)
+        wt, ids = chain.topk_route(router_logits, self.bias, self.scale, self.mode)
+        codes, scales = chain.mxfp4_quant(x)
+        plan = plan_dispatch(ids, wt, self.world, self.experts, self.placement)
+        recv_counts = exchange_counts(plan.send_counts, self.group)
+        src_token = plan.order // TOPK
+        r_codes = all_to_all_rows(codes.index_select(0, src_token), plan.send_counts, recv_counts, self.group)
+        r_scales = all_to_all_rows(scales.index_select(0, src_token), plan.send_counts, recv_counts, self.group)
+        meta = torch.stack([plan.local_expert, plan.weight.view(torch.int32)], dim=1)
+        r_meta = all_to_all_rows(meta, plan.send_counts, recv_counts, self.group)
+        self.last_recv_rows = r_codes.shape[0]
+        y = self.experts_on_rows(r_codes, r_scales, r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32))
+        back = all_to_all_rows(y, recv_counts, plan.send_counts, self.group)
+        slots = scatter_combined(back, plan, tokens)
+        return slots if return_partials else chain.reduce_slots(slots.contiguous())

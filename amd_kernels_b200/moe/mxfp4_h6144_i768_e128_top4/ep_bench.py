@@ -1,0 +1,133 @@
+"""The multi-GPU leg of bench.py: the expert-parallel layer, one process per GPU under torchrun, NCCL over NVLink.
+
+Workload: global T tokens (default 16384) split evenly over the W ranks; 128/W experts per rank; every step is one
+layer call on every rank (route, quantise, all-to-all dispatch, grouped GEMMs, all-to-all combine, fixed-order reduce).
+Total work is fixed as W grows ("strong" scaling). Per-step device time is taken with CUDA events on each rank after an
+untimed L2 flush; the job's time is the maximum over the ranks of the summed step times."""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+H, E, TOPK = 6144, 128, 4
+ROW_BYTES_OUT, ROW_BYTES_IN = 2 * H, H // 2 + H // 32 + 8
+NVLINK_GBS_MEASURED = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool
+N_INPUTS = 4
+
+
+def build_rank_layer(rank, world, placement, seed=0):
+    from oracle import moe_oracle as orc
+    from . import chain, ep
+    (w13, s13, w2, s2), _ = orc.make_weights(seed=seed)
+    mine = ep.local_expert_ids(rank, world, placement=placement).numpy()
+    w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(np.ascontiguousarray(a[mine])).cuda()
+                                                     for a in (w13, s13, w2, s2)))
+    del w13, s13, w2, s2
+    return ep.ExpertParallelMoe(w, None, bias=None, routing_mode="softmax", scale=1.0, placement=placement)
+
+
+def run(args):
+    from . import chain
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    tokens_global = args.tokens or 16384
+    if tokens_global % world:
+        raise ValueError("the global token count must divide evenly over the ranks")
+    t_loc = tokens_global // world
+    zipf = bool(getattr(args, "zipf", False))
+    placement = "interleaved" if zipf else "contiguous"
+    layer = build_rank_layer(rank, world, placement)
+    gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
+    xs = [torch.randn((t_loc, H), device="cuda", generator=gen).bfloat16() for _ in range(N_INPUTS)]
+    lgs = [torch.randn((t_loc, E), device="cuda", generator=gen) for _ in range(N_INPUTS)]
+    if zipf:
+        skew = -2.2 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
+        lgs = [lg + skew for lg in lgs]
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    hx = [t.cpu().pin_memory() for t in xs]
+    hl = [t.cpu().pin_memory() for t in lgs]
+    hout = torch.empty((t_loc, H), dtype=torch.bfloat16).pin_memory()
+
+    def step(i):
+        return layer.forward(xs[i % N_INPUTS], lgs[i % N_INPUTS])
+
+    def e2e_step(i):
+        x = hx[i % N_INPUTS].cuda(non_blocking=True)
+        lg = hl[i % N_INPUTS].cuda(non_blocking=True)
+        hout.copy_(layer.forward(x, lg), non_blocking=True)
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            flush.fill_(i)
+            fn(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        recv = []
+        for i in range(steps):
+            flush.fill_(i)
+            ev[i][0].record()
+            fn(warmup + i)
+            ev[i][1].record()
+            recv.append(layer.last_recv_rows)
+        torch.cuda.synchronize()
+        dist.barrier()
+        wall = time.perf_counter() - t0
+        ms = sum(a.elapsed_time(b) for a, b in ev)
+        both = torch.tensor([ms, wall * 1e3, float(max(recv)), float(sum(recv)) / steps], device="cuda", dtype=torch.float64)
+        mx = both.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = both.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        return mx[0].item(), mx[1].item(), mx[2].item(), sm[3].item() / world
+
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))))
+    from bench import ClockSampler, workload_config, FLOPS_PER_TOKEN, measured_peaks
+    clocks = ClockSampler(local)
+    with clocks:
+        total_ms, wall_ms, max_rows, mean_rows = timed(step, args.steps, args.warmup)
+        e2e_ms, _, _, _ = timed(e2e_step, args.steps, 1)
+    status = torch.tensor([chain.last_status()], device="cuda")
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        if int(status.item()):
+            raise RuntimeError("a kernel reported a device-side status on some rank")
+        per_step = total_ms / args.steps
+        peaks = measured_peaks()
+        remote = (world - 1) / world  # share of a rank's rows that leave it under uniform routing
+        link_bytes = mean_rows * remote * (ROW_BYTES_IN + ROW_BYTES_OUT)
+        t_link = link_bytes / (NVLINK_GBS_MEASURED * 1e9)
+        t_fp4 = tokens_global / world * FLOPS_PER_TOKEN / (4 * peaks["bf16_tflops"] * 1e12)
+        cfg = workload_config(tokens_global, world)
+        cfg.update({"tokens_per_rank": t_loc, "expert_placement": placement, "routing_skew": "zipf 1.1" if zipf else "none",
+                    "max_rows_received_by_a_rank": max_rows, "mean_rows_received_per_rank": mean_rows,
+                    "timing": "CUDA events per step on every rank after an untimed 512 MB L2 flush, max over ranks"})
+        line = {"metric": "moe_layer_tokens_per_s", "value": tokens_global / (per_step * 1e-3), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4", "data": "synthetic",
+                "config": cfg,
+                "roofline": {"kernel": "expert-parallel step (dispatch all-to-all + grouped GEMMs + combine all-to-all)",
+                             "bound": "nvlink" if t_link > t_fp4 else "tensor", "unit": "us",
+                             "nvlink_us": t_link * 1e6, "fp4_us": t_fp4 * 1e6, "achieved": per_step * 1e3,
+                             "peak": max(t_link, t_fp4) * 1e6, "frac": max(t_link, t_fp4) * 1e3 / per_step,
+                             "nvlink_bytes_per_rank_per_direction": link_bytes, "nvlink_gbs_peak": NVLINK_GBS_MEASURED,
+                             "traffic": None},
+                "cpu_baseline": None,
+                "e2e": {"value": tokens_global / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                        "h2d_bytes_per_step": tokens_global * (2 * H + 4 * E), "d2h_bytes_per_step": tokens_global * 2 * H},
+                "gpu_launches": args.steps * 8, "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks.summary()}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

@@ -188,7 +188,8 @@ class Layer:
         return sum(n) / len(n)
 
     def launches_per_step(self):
-        return 7 + (1 if self.tokens * TOPK > 1024 else 0)
+        # route+sort fused up to 32 tokens, split above (plus a count pass above 256), quantise+gather, two GEMMs, reduce
+        return 5 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
 
 
 def time_steps(torch, fn, steps, warmup, flush):
@@ -326,6 +327,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--zipf", action="store_true", help="multi-GPU: the skewed-routing configuration (logit bias -2.2 ln rank)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

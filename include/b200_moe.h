@@ -84,7 +84,7 @@ size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
 int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
                     float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
 
-/* Router top-4 on plain fp32 logits [T][num_experts] followed by the routing sort; one single-CTA kernel up to 256
+/* Router top-4 on plain fp32 logits [T][num_experts] followed by the routing sort; one single-CTA kernel up to 32
  * tokens, b200moe_route_topk + b200moe_permute above (the fused top-k + sort of the reference's small tier,
  * MOE/router_topk_sorted.py:43). Outputs of both. */
 int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, int num_experts, int mode, float scale,

@@ -258,3 +258,33 @@ def test_entry_errors_and_warm_up(C, layer):
     with pytest.raises(ValueError):
         C.mxfp4_moe_experts((torch.zeros((0, 3072), dtype=torch.uint8, device="cuda"), None), None, None, w)
     C.warm_up_mxfp4_moe(w, partials=True)
+
+
+def _single_rank_group():
+    import socket
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    return dist
+
+
+@pytest.mark.parametrize("tokens", [3, 300])
+def test_expert_parallel_path_equals_the_layer_bit_for_bit(C, layer, tokens):
+    """The expert-parallel code path (plan, all-to-all, grouped GEMMs on received rows, combine) with every expert on
+    one rank gives the single-GPU layer's bits: a (token, slot) row does not depend on the batch it is computed in."""
+    from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import ep
+    _single_rank_group()
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(77 + tokens)
+    xb, lg = orc.make_inputs(gen, tokens)
+    x, logits = bf16_dev(xb), dev(lg)
+    par = ep.ExpertParallelMoe(w, None, routing_mode="softmax", scale=1.0)
+    out = par.forward(x, logits)
+    slots = par.forward(x, logits, return_partials=True)
+    ref_slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0 and par.last_recv_rows == 4 * tokens
+    assert torch.equal(slots, ref_slots) and torch.equal(out, C.mxfp4_moe(x, w, router_logits=logits))
