@@ -41,7 +41,7 @@ PREFILL_SWEEP = (2048, 8192)
 N_INPUTS = 8
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch at T=256, from the ncu capture summarised under
 # profiles/ (None until a capture exists)
-NCU_GEMM1_TRAFFIC_BYTES = None
+NCU_GEMM1_TRAFFIC_BYTES = 659_817_984  # profiles/grouped_gemm_t256_ncu_full.md: 652,665,088 read + 7,152,896 written
 
 
 def measured_peaks():
