@@ -9,7 +9,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
-E_ARG, E_ALIGN, E_DRIVER = -1, -2, -3
+E_ARG, E_ALIGN, E_DRIVER, E_TOO_LARGE = -1, -2, -3, -4
 DEV_TIMEOUT = 1
 ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
 
@@ -32,6 +32,7 @@ SIGNATURES = {
     "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_permute": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
+    "b200moe_permute_static": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P]),
     "b200moe_route_sort": (c_int, [_P, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P, _P, _P]),
     "b200moe_quant_dispatch": (c_int, [_P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
@@ -72,6 +73,8 @@ def check(code: int, what: str) -> None:
         return
     if code in (E_ARG, E_ALIGN):
         raise ValueError(f"{what}: rejected argument ({'alignment' if code == E_ALIGN else 'size, pointer or block height'})")
+    if code == E_TOO_LARGE:
+        raise ValueError(f"{what}: more tokens than the allocation-free entry point supports")
     if code == E_DRIVER:
         raise RuntimeError(f"{what}: the CUDA driver cannot encode tensor maps")
     raise RuntimeError(f"{what}: CUDA error {code}")

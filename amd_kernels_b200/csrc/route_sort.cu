@@ -4,6 +4,8 @@
 //
 // Determinism: counts are order-free; placement ranks come from warp match/popc and fixed-order prefix sums, so the row
 // order inside an expert is the pair order 4*token+slot on every run.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -360,4 +362,49 @@ extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_
     B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SOFTMAX>), 1, kChunk, 0, s, logits, bias, static_cast<int>(tokens),
                    num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, num_valid);
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------------ allocation-free sort
+// Some hosts of this library may not allocate device memory around a call: a serving engine that hands every plugin a
+// fixed memory budget at start-up and forbids cudaMalloc afterwards (it synchronises the whole device and would stall
+// the other streams), or code that runs while a stream is being captured, where an allocation is an error. For them the
+// chunk-count scratch of the routing sort lives in the library image itself. Every GPU that loads the library carries
+// these 16 KB until the process exits.
+namespace b200moe {
+constexpr int kStaticSortTokens = B200MOE_STATIC_SORT_MAX_TOKENS;
+constexpr int kStaticSortChunks = kStaticSortTokens * kTopK / kChunk;
+static __device__ __align__(256) int32_t g_sort_scratch[kStaticSortChunks * kMaxE];
+
+// The device address of g_sort_scratch on the CURRENT device. In host code the symbol's name is only a handle, so the
+// address is looked up once per device (with that device current) and remembered.
+static int static_sort_scratch(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int32_t* ptrs[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return B200MOE_E_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sort_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ptrs[dev] = static_cast<int32_t*>(p);
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+}  // namespace b200moe
+
+extern "C" int b200moe_permute_static(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
+                                      int32_t* sorted_ids, float* sorted_w, int32_t* block_expert, int32_t* num_valid,
+                                      void* stream) {
+  using namespace b200moe;
+  if (tokens > kStaticSortTokens) return B200MOE_E_TOO_LARGE;
+  int32_t* scratch = nullptr;
+  const int r = static_sort_scratch(&scratch);
+  if (r) return r;
+  // The count pass writes every entry the placement pass reads, so nothing in the array has to start at zero.
+  return b200moe_permute(ids, w, tokens, num_experts, bm, sorted_ids, sorted_w, block_expert, num_valid, scratch, stream);
 }

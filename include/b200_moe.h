@@ -41,6 +41,8 @@ extern "C" {
 #define B200MOE_E_ARG (-1)     /* null pointer, size out of range, unsupported bm */
 #define B200MOE_E_ALIGN (-2)   /* a pointer that must be 16-byte (workspace: 256-byte) aligned is not */
 #define B200MOE_E_DRIVER (-3)  /* the CUDA driver entry point for tensor maps is unavailable */
+#define B200MOE_E_TOO_LARGE (-4) /* more tokens than the allocation-free entry point's built-in scratch holds */
+#define B200MOE_STATIC_SORT_MAX_TOKENS 8192
 #define B200MOE_DEV_TIMEOUT 1  /* a bounded mbarrier wait ran out inside a kernel */
 #define B200MOE_DEV_BAD_INDEX 2 /* a block count or expert id read from the routing table was out of range */
 
@@ -83,6 +85,18 @@ int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, uint8_t* code
 size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
 int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
                     float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
+
+/* The routing sort for callers that cannot allocate device memory (no counterpart in the reference, whose hosts allocate
+ * every scratch buffer with torch.empty). Same inputs, outputs and results as b200moe_permute, but the chunk-count scratch
+ * is a 16 KB array inside the library image instead of a caller buffer; the call performs no cudaMalloc / cudaFree and
+ * calls no allocating routine. Limit: tokens <= B200MOE_STATIC_SORT_MAX_TOKENS (8192), otherwise B200MOE_E_TOO_LARGE.
+ * Every GPU that loads the library holds the array until the process exits. The first call on a device looks up the
+ * array's device address (that device must be current, and `stream` must belong to it): make that first call before any
+ * stream capture begins. All calls on one device share the array and it keeps the previous call's contents (nothing in
+ * it needs clearing: the count pass overwrites every entry the placement pass reads), so two calls that overlap on the
+ * GPU -- different streams, no ordering between them -- race; order them or use b200moe_permute with separate scratch. */
+int b200moe_permute_static(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
+                           int32_t* sorted_ids, float* sorted_w, int32_t* block_expert, int32_t* num_valid, void* stream);
 
 /* Router top-4 on plain fp32 logits [T][num_experts] followed by the routing sort; one single-CTA kernel up to 32
  * tokens, b200moe_route_topk + b200moe_permute above (the fused top-k + sort of the reference's small tier,
