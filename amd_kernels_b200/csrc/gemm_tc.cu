@@ -104,6 +104,19 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]),
+        "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]),
+        "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // AND of a predicate over the 128 epilogue threads (named barrier 1); every one of them gets the result.
 __device__ __forceinline__ bool epilogue_all(bool ok) {
   uint32_t out;
@@ -137,7 +150,10 @@ struct Cfg {
   static constexpr int kBOffset = kTileRecordBytes;
   static constexpr int kSfbOffset = kBOffset + kBBytes;
   static constexpr int kStageBytes = kSfbOffset + kSfBytes;
-  static constexpr int kStages = MODE == 1 ? (BM == 128 ? 5 : (BM == 64 ? 6 : 8)) : (BM == 128 ? 5 : 8);
+  // bm = 128 (prefill): the token block is the 128-row M operand and the weight tile is N, so a TMEM lane is a token and
+  // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
+  static constexpr bool kTokensAreM = BM == 128;
+  static constexpr int kStages = BM == 128 ? 6 : (MODE == 1 && BM == 64 ? 6 : 8);
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   static constexpr int kSfaCol = 2 * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
@@ -149,7 +165,8 @@ struct Cfg {
   // GEMM2 epilogue staging: up to 32 token columns x (128 output columns + 4 pad) floats
   static constexpr int kOutCols = BM < 32 ? BM : 32;
   static constexpr int kOutRowFloats = 132;
-  static constexpr int kEpiBytes = MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : kOutCols * kOutRowFloats * 4;
+  static constexpr int kEpiBytes =
+      kTokensAreM ? 0 : (MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : kOutCols * kOutRowFloats * 4);
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;  // + slack to align to 1024 bytes
   static constexpr int kActAtomsPerBlock = MODE == 1 ? kH / 128 : kI / 128;  // activation scale atoms per row block
   static constexpr int kActRowBytes = MODE == 1 ? kH / 2 : kI / 2;
@@ -291,8 +308,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             // 64 elements = 32 bytes per MMA; scales: atom k/2, bytes {0,1} or {2,3} of each row's 4-byte cell
             const uint32_t sf_id = (k & 1) * 2u;
             const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
-            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
-                        tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
+            if (C::kTokensAreM)
+              tc_mma_mxf4(d_tmem, db + 2u * k, da + 2u * k, idesc, tmem_base + C::kSfbCol + 4 * (k >> 1),
+                          tmem_base + C::kSfaCol + 4 * (k >> 1), (kt | k) != 0);
+            else
+              tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
+                          tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
           }
           tc_commit(smem_u32(&bar_empty[s]));
         }
@@ -302,14 +323,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, TMEM lane quarter = warp % 4)
     const int q = warp & 3;
-    const int et = threadIdx.x - 64;  // 0..127
+    const int et = threadIdx.x - 64;  // 0..127, work-item index
+    const int tr = q * 32 + lane;     // the TMEM lane this thread reads (warps 2..5 own quarters 2, 3, 0, 1)
     float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + C::kStages * C::kStageBytes);
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
-      if (MODE == 2 && et < BM) {  // this block's rows: fetched before the wait so the latency hides behind the MMAs
+      int my_sid = 0;
+      float my_wt = 0.0f;
+      if (MODE == 2 && C::kTokensAreM) {  // one token row per thread; fetched before the wait, hidden behind the MMAs
+        my_sid = __ldcg(ep.sorted_ids + row0 + tr);
+        my_wt = __ldcg(ep.sorted_w + row0 + tr);
+      } else if (MODE == 2 && et < BM) {
         s_sid[et] = __ldcg(ep.sorted_ids + row0 + et);
         s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
       }
@@ -317,7 +344,70 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status))) break;
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
-      if (MODE == 1) {
+      if (C::kTokensAreM && MODE == 1) {
+        // lane = token row tr of the block; columns = tile rows: [gate 32 | up 32 | gate 32 | up 32] of 64 intermediate
+        // columns. Everything is thread-local: SwiGLU, the two block maxima, 2 x 32 codes -> two 16-byte stores.
+#pragma unroll 1
+        for (int g = 0; g < 2; ++g) {
+          uint32_t gv[32], uv[32];
+          tc_ld32(t_acc + 64 * g, gv);
+          tc_ld32(t_acc + 64 * g + 32, uv);
+          if (g == 1) {  // accumulator fully read: hand the TMEM buffer back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          float h[32];
+          float amax = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            h[k] = swiglu_oai(__uint_as_float(gv[k]), __uint_as_float(uv[k]));
+            amax = fmaxf(amax, fabsf(h[k]));
+          }
+          const int sc = quark_even_e8m0(amax);
+          const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
+          uint32_t words[4];
+#pragma unroll
+          for (int wd = 0; wd < 4; ++wd) {
+            uint32_t acc_w = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
+            words[wd] = acc_w;
+          }
+          const int grp = 2 * mt + g;
+          *reinterpret_cast<uint4*>(ep.hq + (row0 + tr) * (kI / 2) + grp * 16) =
+              make_uint4(words[0], words[1], words[2], words[3]);
+          ep.sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(tr, grp & 3)] =
+              static_cast<uint8_t>(sc);
+        }
+      } else if (C::kTokensAreM) {
+        // lane = token row tr; columns = 128 output columns of this W2 tile: scale, round to bf16, 16-byte stores
+        const int64_t token = my_sid & 0x00ffffff;
+        const bool live = token < ep.tokens;
+        __nv_bfloat16* dst = ep.slots + (token * kTopK + ((my_sid >> 24) & 3)) * kH + mt * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tc_ld32(t_acc + 32 * c, v);
+          if (c == 3) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          if (live) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[8 * k + 2 * j]) * my_wt,
+                                                                __uint_as_float(v[8 * k + 2 * j + 1]) * my_wt);
+                o[j] = *reinterpret_cast<const uint32_t*>(&p2);
+              }
+              *reinterpret_cast<uint4*>(dst + 32 * c + 8 * k) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      } else if (MODE == 1) {
         // TMEM lanes of a tile: quarter 0 = gate i 0..31, 1 = up i 0..31, 2 = gate i 32..63, 3 = up i 32..63.
         // Stage the accumulators as [token][group][32 gate | 32 up | pad] so one thread owns one (token, 32-column
         // group): SwiGLU, the block maximum and the 32 codes are thread-local and the codes leave as one 16-byte store.

@@ -60,36 +60,40 @@ __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __res
     *reinterpret_cast<uint32_t*>(sdst + a * kAtomBytes) = pad ? 0x7f7f7f7fu : ssrc[a];
 }
 
-// Quantisation fused with the gather: one warp per sorted row reads the token's bf16 row, quantises it and writes the
-// codes in sorted order and the scales into the block's atoms (a token is quantised once per slot; the reads hit L2).
+// Quantisation fused with the gather: one 256-thread CTA per sorted row reads the token's bf16 row (three 16-byte loads
+// per thread, all in flight at once), quantises it and writes the codes in sorted order and the scales into the block's
+// atoms (a token is quantised once per slot; the repeated reads hit L2).
 __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __restrict__ x,
                                                              const int32_t* __restrict__ sorted_ids,
                                                              const int32_t* __restrict__ num_valid, int64_t tokens,
                                                              int bm_shift, uint8_t* __restrict__ xq_sorted,
                                                              uint8_t* __restrict__ sfx) {
   pdl_enter(x, sorted_ids, num_valid);
+  constexpr int kIters = kH / 8 / 256;  // 3
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t row = blockIdx.x;
   if (row >= __ldcg(num_valid)) return;
   const int64_t token = __ldcg(sorted_ids + row) & 0x00ffffff;
-  const bool pad = token >= tokens;
-  const uint4* src = x + token * (kH / 8);
   uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + row * (kH / 2));
   const int r = static_cast<int>(row & ((1 << bm_shift) - 1));
   uint8_t* sdst = sfx + (row >> bm_shift) * (kH / 128) * kAtomBytes + atom_offset(r, 0);
-  if (pad) {  // a padding row: zero codes, the scale byte of an all-zero block
-#pragma unroll 4
-    for (int it = 0; it < kH / 8 / 32; ++it) {
-      dst[it * 32 + lane] = 0u;
-      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (it * 2 + (lane >> 4)) * kAtomBytes) = 0x01010101u;
+  if (token >= tokens) {  // a padding row: zero codes, the scale byte of an all-zero block
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) {
+      const int idx = it * 256 + threadIdx.x;
+      dst[idx] = 0u;
+      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = 0x01010101u;
     }
     return;
   }
-#pragma unroll 4
-  for (int it = 0; it < kH / 8 / 32; ++it) {
-    const int idx = it * 32 + lane;
-    const uint4 raw = __ldcg(src + idx);
-    const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint4* src = x + token * (kH / 8);
+  uint4 raw[kIters];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) raw[it] = __ldcg(src + it * 256 + threadIdx.x);
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const uint32_t rr[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
     float v[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -107,11 +111,11 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
 #pragma unroll
     for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
     dst[idx] = packed;
-    // 8 blocks of 32 per warp step = 2 atoms' worth of 4 scale bytes: lanes 0 and 16 gather 4 neighbours' bytes
+    // 4 lanes share a 32-element block, 16 lanes one scale atom's 4 bytes: lanes 0 and 16 gather their neighbours' bytes
     uint32_t sc = static_cast<uint32_t>(e);
     sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
     sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
-    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (it * 2 + (lane >> 4)) * kAtomBytes) = sc;
+    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = sc;
   }
 }
 
@@ -156,7 +160,7 @@ extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_
       (reinterpret_cast<uintptr_t>(sfx) & 15))
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
-  const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
+  const unsigned grid = static_cast<unsigned>(max_rows);
   B200MOE_LAUNCH(quant_dispatch_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx);
   return 0;
 }
