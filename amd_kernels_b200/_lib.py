@@ -28,6 +28,8 @@ SIGNATURES = {
     "b200moe_block_rows": (c_int, [c_int64]),
     "b200moe_preshuffle_w13": (c_int, [_P, _P, c_int, _P, _P]),
     "b200moe_preshuffle_w2": (c_int, [_P, _P, c_int, _P, _P]),
+    "b200moe_router_splits": (c_int, [c_int64]),
+    "b200moe_router_gemm": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P]),
     "b200moe_route_topk": (c_int, [_P, c_int64, c_int64, c_int, _P, c_int64, c_int, c_int, c_float, _P, _P, _P]),
     "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
@@ -41,6 +43,7 @@ SIGNATURES = {
     "b200moe_gemm1_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P]),
     "b200moe_reduce_slots": (c_int, [_P, _P, c_int64, _P, _P]),
+    "b200moe_reduce_rows": (c_int, [_P, _P, _P, c_int64, _P, _P]),
     "b200moe_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_forward": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, c_size_t, _P, _P, _P, _P]),
     "b200moe_forward_host": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, _P, _P, c_size_t, _P, _P, _P, _P, _P]),

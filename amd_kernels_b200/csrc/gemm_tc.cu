@@ -7,7 +7,7 @@
 //
 //   warp 0    producer: one thread issues TMA tile loads (128B-swizzled FP4 tiles) and bulk copies of scale atoms
 //   warp 1    MMA: allocates TMEM; one thread copies scale atoms to TMEM (tcgen05.cp) and issues tcgen05.mma
-//   warps 2-5 epilogue: tcgen05.ld of the accumulator, then
+//   warps 2-5 epilogue (bm = 128: a second group, warps 6-9, takes every other unit): tcgen05.ld of the accumulator, then
 //             GEMM1: SwiGLU-OAI (gate and up rows of one tile live in neighbouring lane quarters), MXFP4 requantisation
 //                    of 32 intermediate columns = the 32 lanes of a warp, codes and scale atoms to global memory
 //             GEMM2: times the routing weight, bf16, one store per (token, slot, column)
@@ -117,13 +117,13 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// AND of a predicate over the 128 epilogue threads (named barrier 1); every one of them gets the result.
-__device__ __forceinline__ bool epilogue_all(bool ok) {
+// AND of a predicate over the 128 threads of one epilogue group (named barrier 1 or 2); every one of them gets the result.
+__device__ __forceinline__ bool epilogue_all(bool ok, uint32_t barrier_id) {
   uint32_t out;
   asm volatile(
-      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, 1, 128, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, %2, 128, q;\nselp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(out)
-      : "r"(static_cast<uint32_t>(ok))
+      : "r"(static_cast<uint32_t>(ok)), "r"(barrier_id)
       : "memory");
   return out != 0;
 }
@@ -154,6 +154,9 @@ struct Cfg {
   // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
   static constexpr bool kTokensAreM = BM == 128;
   static constexpr int kStages = BM == 128 ? 6 : (MODE == 1 && BM == 64 ? 6 : 8);
+  // bm = 128 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
+  static constexpr int kEpiGroups = kTokensAreM ? 2 : 1;
+  static constexpr int kThreads = 64 + 128 * kEpiGroups;
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   static constexpr int kSfaCol = 2 * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
@@ -183,10 +186,9 @@ struct EpilogueArgs {
   int64_t tokens;
 };
 
-constexpr int kThreads = 192;
 
 template <int MODE, int BM>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                         const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
                         const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status, int num_experts,
@@ -321,13 +323,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 2..5, TMEM lane quarter = warp % 4)
+    // ---------------------------------------------------------------- epilogue (groups of 4 warps, TMEM lane quarter = warp % 4)
     const int q = warp & 3;
-    const int et = threadIdx.x - 64;  // 0..127, work-item index
+    const int group = (warp - 2) >> 2;                   // epilogue group 0 or 1
+    const int et = (threadIdx.x - 64) & 127;             // 0..127, work-item index inside the group
     const int tr = q * 32 + lane;     // the TMEM lane this thread reads (warps 2..5 own quarters 2, 3, 0, 1)
     float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + C::kStages * C::kStageBytes);
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
+      if (C::kEpiGroups == 2 && static_cast<int>(ui & 1u) != group) continue;  // group g owns accumulator buffer g
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
@@ -341,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
       }
       // the four warps must agree before they meet at the named barrier below
-      if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status))) break;
+      if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status), 1u + group)) break;
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       if (C::kTokensAreM && MODE == 1) {
@@ -566,7 +570,7 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
   const int64_t max_units = max_rows / BM * C::kTilesM;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   if (grid <= 0) return 0;
-  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
+  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
 

@@ -315,6 +315,18 @@ def reduce_slots(slots: torch.Tensor, shared: torch.Tensor | None = None) -> tor
     return out
 
 
+def reduce_rows(rows: torch.Tensor, index: torch.Tensor, tokens: int) -> torch.Tensor:
+    """bf16 rows [N, 6144] + int32 index [M, 4] (row of pair 4*token+slot) -> bf16 [M, 6144], slots 0..3 in fp32."""
+    if rows.dtype != torch.bfloat16 or rows.ndim != 2 or rows.shape[1] != H or not rows.is_contiguous():
+        raise ValueError("expected contiguous BF16 [N, 6144]")
+    if index.dtype != torch.int32 or index.numel() != tokens * TOPK or not index.is_contiguous():
+        raise ValueError("expected a contiguous int32 index of 4 entries per token")
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device=rows.device)
+    _lib.check(_lib.load().b200moe_reduce_rows(_ptr(rows), _ptr(index), None, tokens, _ptr(out), _stream(rows.device)),
+               "reduce_rows")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ the entry
 def _logits(x, w, router_logits):
     if router_logits is not None:
@@ -323,8 +335,22 @@ def _logits(x, w, router_logits):
         return router_logits.contiguous()
     if w.router_weight is None:
         raise ValueError("needs router_logits= or MoeWeights with router_weight")
-    # plain library GEMM in fp32 (the bf16x3 split-K router kernel of the reference is not rebuilt)
-    return torch.matmul(x.float(), w.router_weight.float().t()).contiguous()
+    return router_gemm_partials(x, w.router_weight)
+
+
+def router_gemm_partials(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """bf16 x [M, 6144] times the fp32 gate [E, 6144] -> split-K partials as an [M, S, E] view of [S, M, E] (the layout
+    the reference's routers write, router_gemm.py:390-467); ``topk_route`` adds them in split order."""
+    if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expected contiguous BF16 [M,6144]")
+    if gate.dtype != torch.float32 or gate.ndim != 2 or gate.shape[1] != H or not gate.is_contiguous():
+        raise ValueError("expected a contiguous fp32 gate [E, 6144]")
+    lib = _lib.load()
+    m, n_exp = x.shape[0], gate.shape[0]
+    splits = int(lib.b200moe_router_splits(m))
+    parts = torch.empty((splits, m, n_exp), dtype=torch.float32, device=x.device)
+    _lib.check(lib.b200moe_router_gemm(_ptr(x), _ptr(gate), m, n_exp, splits, _ptr(parts), _stream(x.device)), "router_gemm")
+    return parts.permute(1, 0, 2)
 
 
 def route(x, w, router_logits=None):
@@ -359,6 +385,13 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     lib = _lib.load()
     n, dev = x.shape[0], x.device
     logits = _logits(x, w, router_logits)
+    if logits.ndim == 3:
+        # split-K partials from the router GEMM: the top-4 kernel adds them in split order, then the stages run one by one
+        wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
+        sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
+        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w)
+        slots = grouped_gemm2(hq, sfh, sort, w)
+        return (slots, None) if return_partials else reduce_slots(slots)
     ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     slots = torch.empty((n, TOPK, H), dtype=torch.bfloat16, device=dev)

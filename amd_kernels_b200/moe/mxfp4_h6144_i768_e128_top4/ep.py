@@ -97,22 +97,15 @@ class ExpertParallelMoe:
         self.bias, self.mode, self.scale, self.placement, self.experts = bias, routing_mode, float(scale), placement, experts
         self.last_recv_rows = 0
 
-    def experts_on_rows(self, codes, scales, local_expert, weight):
-        """The grouped GEMMs on rows that arrived from any rank: row r -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r."""
+    def experts_on_rows(self, codes, scales, local_expert, weight, n):
+        """The grouped GEMMs on rows that arrived from any rank: row r < n -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r.
+        The buffers hold a multiple of four rows (rows beyond n carry expert id -1 and are dropped by the sort)."""
         from . import chain
-        n = codes.shape[0]
+        groups = codes.shape[0] // TOPK  # rows are handed to the sort as pseudo-tokens of four pairs
         if n == 0:
             return torch.empty((0, H), dtype=torch.bfloat16, device=codes.device)
-        groups = (n + TOPK - 1) // TOPK  # rows are handed to the sort as pseudo-tokens of four pairs
-        pad = groups * TOPK - n
-        if pad:
-            local_expert = torch.cat([local_expert, local_expert.new_full((pad,), -1)])  # ids outside the range are dropped
-            weight = torch.cat([weight, weight.new_zeros(pad)])
-            codes = torch.cat([codes, codes.new_zeros((pad, codes.shape[1]))])
-            scales = torch.cat([scales, scales.new_zeros((pad, scales.shape[1]))])
         bm = chain.variant_for(groups)
-        sort = chain.moe_sort(local_expert.view(groups, TOPK).contiguous(), weight.view(groups, TOPK).contiguous(), bm,
-                              self.w.num_experts)
+        sort = chain.moe_sort(local_expert.view(groups, TOPK), weight.view(groups, TOPK), bm, self.w.num_experts)
         xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
         hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
         slots = chain.grouped_gemm2(hq, sfh, sort, self.w)
@@ -125,15 +118,37 @@ class ExpertParallelMoe:
         chain.variant_for(tokens)
         wt, ids = chain.topk_route(router_logits, self.bias, self.scale, self.mode)
         codes, scales = chain.mxfp4_quant(x)
-        plan = plan_dispatch(ids, wt, self.world, self.experts, self.placement)
-        recv_counts = exchange_counts(plan.send_counts, self.group)
-        src_token = plan.order // TOPK
-        r_codes = all_to_all_rows(codes.index_select(0, src_token), plan.send_counts, recv_counts, self.group)
-        r_scales = all_to_all_rows(scales.index_select(0, src_token), plan.send_counts, recv_counts, self.group)
-        meta = torch.stack([plan.local_expert, plan.weight.view(torch.int32)], dim=1)
-        r_meta = all_to_all_rows(meta, plan.send_counts, recv_counts, self.group)
-        self.last_recv_rows = r_codes.shape[0]
-        y = self.experts_on_rows(r_codes, r_scales, r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32))
-        back = all_to_all_rows(y, recv_counts, plan.send_counts, self.group)
-        slots = scatter_combined(back, plan, tokens)
-        return slots if return_partials else chain.reduce_slots(slots.contiguous())
+        # where every pair goes; the row counts cross the ranks and reach the host in one read
+        dest, local = expert_owner(ids.reshape(-1).long(), self.world, self.experts, self.placement)
+        order = torch.argsort(dest, stable=True)
+        counts = torch.bincount(dest, minlength=self.world)
+        arrived = torch.empty_like(counts)
+        dist.all_to_all_single(arrived, counts, group=self.group)
+        send_counts, recv_counts = torch.stack([counts, arrived]).tolist()
+        n = sum(recv_counts)
+        padded = (n + TOPK - 1) // TOPK * TOPK
+        self.last_recv_rows = n
+        src_token = order // TOPK
+        meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32)], dim=1)
+
+        def exchange(rows, width, dtype, fill=None):
+            out = torch.empty((padded, width), dtype=dtype, device=x.device)
+            if fill is not None and padded > n:
+                out[n:] = fill
+            dist.all_to_all_single(out[:n], rows.contiguous(), output_split_sizes=recv_counts,
+                                   input_split_sizes=send_counts, group=self.group)
+            return out
+
+        r_codes = exchange(codes.index_select(0, src_token), H // 2, torch.uint8, 0)
+        r_scales = exchange(scales.index_select(0, src_token), H // 32, torch.uint8, 0)
+        r_meta = exchange(meta, 2, torch.int32, -1)
+        y = self.experts_on_rows(r_codes, r_scales, r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32), n)
+        back = torch.empty((tokens * TOPK, H), dtype=torch.bfloat16, device=x.device)
+        dist.all_to_all_single(back, y.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts,
+                               group=self.group)
+        # pair q sits in row where[q] of what came back (send order); the reduce reads through that index
+        where = torch.empty(tokens * TOPK, dtype=torch.int32, device=x.device)
+        where[order] = torch.arange(tokens * TOPK, dtype=torch.int32, device=x.device)
+        if return_partials:
+            return back.index_select(0, where.long()).view(tokens, TOPK, H)
+        return chain.reduce_rows(back, where, tokens)

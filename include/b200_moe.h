@@ -65,6 +65,15 @@ int b200moe_block_rows(int64_t tokens);
 int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_scale, int num_experts, uint8_t* w13t, void* stream);
 int b200moe_preshuffle_w2(const uint8_t* w2, const uint8_t* w2_scale, int num_experts, uint8_t* w2t, void* stream);
 
+/* Router GEMM (MOE/router_gemm.py:390-467 router_gemm_partials; oracle MOE/reference.py:101-111): x bf16 [T][6144] times the
+ * fp32 gate [num_experts][6144] as split-K partials fp32 [splits][T][num_experts] (partial s covers K elements
+ * [s*6144/splits, (s+1)*6144/splits)); each partial is within 2^-18 * sum|x||w| of the exact product, results are the
+ * same on every run. b200moe_router_splits(T) is the split count the library uses (16 up to 2048 tokens, 4 above). Feed
+ * the partials to b200moe_route_topk with stride_t = num_experts, stride_s = T*num_experts. */
+int b200moe_router_splits(int64_t tokens);
+int b200moe_router_gemm(const void* x_bf16, const float* gate, int64_t tokens, int num_experts, int splits,
+                        float* partials, void* stream);
+
 /* Router top-4 (MOE/router_topk.py:239-272 splitk_biased_topk). logits[t][e] = sum over s<S of
  * partials[t*stride_t + s*stride_s + e], added from 0.0 in split order; plain logits are S=1. mode SIGMOID_BIAS:
  * s = sigmoid(logit), choice = s + bias[e], weight = s*scale / sum of the 4 chosen s. mode SOFTMAX: choice = logit,
@@ -152,6 +161,13 @@ int b200moe_gemm2_simt(const uint8_t* w2, const uint8_t* w2_scale, const uint8_t
 /* Slot reduce (MOE/common/reduce_slots_shared.py:16-41 reduce_slots_shared; oracle MOE/reference.py:151-159):
  * out = bf16( (((+0 + s0) + s1) + s2) + s3 (+ shared) ) in fp32, bit-exact. shared may be null. */
 int b200moe_reduce_slots(const void* slots_bf16, const void* shared_bf16, int64_t tokens, void* out_bf16, void* stream);
+
+/* The same reduce over slot rows that sit in another order: index int32 [T][4] gives, for pair 4*token+slot, its row in
+ * rows_bf16 [N][6144] (the expert-parallel combine: rows come back from the other ranks in send order). Same arithmetic
+ * and the same bits as b200moe_reduce_slots on the reordered rows. No counterpart in the reference (it has no expert
+ * parallelism); the fixed slot order is that of MOE/reference.py:151-159. */
+int b200moe_reduce_rows(const void* rows_bf16, const int32_t* index, const void* shared_bf16, int64_t tokens,
+                        void* out_bf16, void* stream);
 
 /* The whole routed layer on one stream (MOE/chain.py:127-197 mxfp4_moe without the shared expert): route -> quantise
  * -> sort -> gather -> GEMM1 -> GEMM2 -> (reduce). `workspace` of b200moe_workspace_bytes(T, num_experts) bytes,
