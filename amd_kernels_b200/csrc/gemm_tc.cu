@@ -153,7 +153,7 @@ struct Cfg {
   // bm = 128 (prefill): the token block is the 128-row M operand and the weight tile is N, so a TMEM lane is a token and
   // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
   static constexpr bool kTokensAreM = BM == 128;
-  static constexpr int kStages = BM == 128 ? 6 : (MODE == 1 && BM == 64 ? 6 : 8);
+  static constexpr int kStages = BM == 128 ? (MODE == 1 ? 6 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
   // bm = 128 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
   static constexpr int kEpiGroups = kTokensAreM ? 2 : 1;
   static constexpr int kThreads = 64 + 128 * kEpiGroups;
@@ -168,8 +168,10 @@ struct Cfg {
   // GEMM2 epilogue staging: up to 32 token columns x (128 output columns + 4 pad) floats
   static constexpr int kOutCols = BM < 32 ? BM : 32;
   static constexpr int kOutRowFloats = 132;
-  static constexpr int kEpiBytes =
-      kTokensAreM ? 0 : (MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : kOutCols * kOutRowFloats * 4);
+  // bm = 128 GEMM2: one strip of 32 rows x (128 bytes + 16 pad) per epilogue warp
+  static constexpr int kStripRowBytes = 144;
+  static constexpr int kEpiBytes = kTokensAreM ? (MODE == 2 ? 8 * 32 * kStripRowBytes : 0)
+                                               : (MODE == 1 ? kEpiCols * kEpiRowFloats * 4 : kOutCols * kOutRowFloats * 4);
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;  // + slack to align to 1024 bytes
   static constexpr int kActAtomsPerBlock = MODE == 1 ? kH / 128 : kI / 128;  // activation scale atoms per row block
   static constexpr int kActRowBytes = MODE == 1 ? kH / 2 : kI / 2;
@@ -184,7 +186,30 @@ struct EpilogueArgs {
   const float* sorted_w;
   __nv_bfloat16* slots;
   int64_t tokens;
+  // GEMM2, expert parallel: pair r of this rank's rows belongs to rank row_rank[r], where it is pair row_pair[r];
+  // its result row is stored straight into that rank's slot buffer peer_slots[rank] (a peer mapping over NVLink)
+  const int32_t* row_rank;
+  const int32_t* row_pair;
+  __nv_bfloat16* peer_slots[8];
+  int world;
+  int64_t peer_rows;  // rows of every rank's slot buffer
+  int32_t* status;
 };
+
+// Where the result row of sorted-row entry `sid` goes (null: a padding row).
+__device__ __forceinline__ __nv_bfloat16* slot_row(const EpilogueArgs& ep, int sid) {
+  const int64_t token = sid & 0x00ffffff;
+  if (token >= ep.tokens) return nullptr;
+  const int64_t pair = token * kTopK + ((sid >> 24) & 3);
+  if (ep.row_rank == nullptr) return ep.slots + pair * kH;
+  const int rank = __ldcg(ep.row_rank + pair);
+  const int64_t dst_pair = __ldcg(ep.row_pair + pair);
+  if (rank < 0 || rank >= ep.world || dst_pair < 0 || dst_pair >= ep.peer_rows) {  // never store through a bad index
+    atomicExch(ep.status, B200MOE_DEV_BAD_INDEX);
+    return nullptr;
+  }
+  return ep.peer_slots[rank] + dst_pair * kH;
+}
 
 
 template <int MODE, int BM>
@@ -201,7 +226,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int s_sid[MODE == 2 ? BM : 1];
+  __shared__ __nv_bfloat16* s_dst[MODE == 2 ? BM : 1];
   __shared__ float s_wt[MODE == 2 ? BM : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,6 +266,8 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   launder(num_valid);
   launder(ep.sorted_ids);
   launder(ep.sorted_w);
+  launder(ep.row_rank);
+  launder(ep.row_pair);
   int n_blocks = __ldcg(num_valid) / BM;
   if (n_blocks < 0 || n_blocks > max_blocks) {  // a routing table that does not fit its buffers: record it, do nothing
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
@@ -335,13 +362,13 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
-      int my_sid = 0;
+      __nv_bfloat16* my_dst = nullptr;
       float my_wt = 0.0f;
       if (MODE == 2 && C::kTokensAreM) {  // one token row per thread; fetched before the wait, hidden behind the MMAs
-        my_sid = __ldcg(ep.sorted_ids + row0 + tr);
+        my_dst = slot_row(ep, __ldcg(ep.sorted_ids + row0 + tr));
         my_wt = __ldcg(ep.sorted_w + row0 + tr);
       } else if (MODE == 2 && et < BM) {
-        s_sid[et] = __ldcg(ep.sorted_ids + row0 + et);
+        s_dst[et] = slot_row(ep, __ldcg(ep.sorted_ids + row0 + et));
         s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
       }
       // the four warps must agree before they meet at the named barrier below
@@ -385,31 +412,44 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
               static_cast<uint8_t>(sc);
         }
       } else if (C::kTokensAreM) {
-        // lane = token row tr; columns = 128 output columns of this W2 tile: scale, round to bf16, 16-byte stores
-        const int64_t token = my_sid & 0x00ffffff;
-        const bool live = token < ep.tokens;
-        __nv_bfloat16* dst = ep.slots + (token * kTopK + ((my_sid >> 24) & 3)) * kH + mt * 128;
+        // lane = token row tr; columns = 128 output columns of this W2 tile. Scale, round to bf16, then pass the warp's
+        // 32 rows through its own shared-memory strip so that eight lanes store one row's 128 contiguous bytes: full
+        // lines for local HBM and full-size packets when the row lives in another rank's slot buffer over NVLink.
+        uint8_t* strip = reinterpret_cast<uint8_t*>(stage_f) + (warp - 2) * (32 * C::kStripRowBytes);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tc_ld32(t_acc + 32 * c, v);
-          if (c == 3) {
-            tc_fence_before();
-            mbar_arrive(smem_u32(&bar_tempty[acc]));
-          }
-          if (live) {
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tc_ld32(t_acc + 64 * half + 32 * c, v);
+            if (half == 1 && c == 1) {
+              tc_fence_before();
+              mbar_arrive(smem_u32(&bar_tempty[acc]));
+            }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               uint32_t o[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[8 * k + 2 * j]) * my_wt,
-                                                                __uint_as_float(v[8 * k + 2 * j + 1]) * my_wt);
-                o[j] = *reinterpret_cast<const uint32_t*>(&p2);
+              for (int jj = 0; jj < 4; ++jj) {
+                const __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(v[8 * k + 2 * jj]) * my_wt,
+                                                                __uint_as_float(v[8 * k + 2 * jj + 1]) * my_wt);
+                o[jj] = *reinterpret_cast<const uint32_t*>(&p2);
               }
-              *reinterpret_cast<uint4*>(dst + 32 * c + 8 * k) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(strip + lane * C::kStripRowBytes + c * 64 + k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            const unsigned long long p =
+                __shfl_sync(0xffffffffu, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(my_dst)), r);
+            const uint4 val = *reinterpret_cast<const uint4*>(strip + r * C::kStripRowBytes + (lane & 7) * 16);
+            if (p != 0ull)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(p)) + mt * 128 + half * 64 +
+                                        (lane & 7) * 8) = val;
+          }
+          __syncwarp();
         }
       } else if (MODE == 1) {
         // TMEM lanes of a tile: quarter 0 = gate i 0..31, 1 = up i 0..31, 2 = gate i 32..63, 3 = up i 32..63.
@@ -485,9 +525,8 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
 #pragma unroll 2
           for (int item = et; item < C::kOutCols * 32; item += 128) {
             const int j = item >> 5, seg = item & 31;
-            const int s_id = s_sid[c0 + j];
-            const int64_t token = s_id & 0x00ffffff;
-            if (token < ep.tokens) {
+            __nv_bfloat16* row_dst = s_dst[c0 + j];
+            if (row_dst != nullptr) {
               const float s_w = s_wt[c0 + j];
               const float4 v = *reinterpret_cast<const float4*>(stage_f + j * C::kOutRowFloats + seg * 4);
               const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * s_w, v.y * s_w);
@@ -495,7 +534,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
               uint2 packed;
               packed.x = *reinterpret_cast<const uint32_t*>(&lo);
               packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-              *reinterpret_cast<uint2*>(ep.slots + (token * kTopK + ((s_id >> 24) & 3)) * kH + mt * 128 + seg * 4) = packed;
+              *reinterpret_cast<uint2*>(row_dst + mt * 128 + seg * 4) = packed;
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -614,13 +653,12 @@ extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, 
                       static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
-                                      const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
-                                      const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
-                                      int32_t* status, void* stream) {
+static int gemm2_common(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                        const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                        const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, b200moe::EpilogueArgs ep,
+                        int32_t* status, void* stream) {
   using namespace b200moe;
-  if (!w2t || !hq || !sfh || !block_expert || !num_valid || !sorted_ids || !sorted_w || !slots_bf16 || !status)
-    return B200MOE_E_ARG;
+  if (!w2t || !hq || !sfh || !block_expert || !num_valid || !sorted_ids || !sorted_w || !status) return B200MOE_E_ARG;
   if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || tokens < 0 ||
       (bm != 16 && bm != 32 && bm != 64 && bm != 128) || max_rows % bm)
     return B200MOE_E_ARG;
@@ -629,11 +667,41 @@ extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const
   CUtensorMap mx;
   const int r = make_map(&mx, hq, kI / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
   if (r) return r;
-  EpilogueArgs ep{};
   ep.sorted_ids = sorted_ids;
   ep.sorted_w = sorted_w;
-  ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
   ep.tokens = tokens;
   return launch_bm<2>(bm, mx, w2t, sfh, block_expert, num_valid, ep, max_rows, num_experts, status,
                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                      const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                                      const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
+                                      int32_t* status, void* stream) {
+  if (!slots_bf16) return B200MOE_E_ARG;
+  b200moe::EpilogueArgs ep{};
+  ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
+  return gemm2_common(w2t, num_experts, hq, sfh, block_expert, num_valid, sorted_ids, sorted_w, max_rows, bm, tokens, ep,
+                      status, stream);
+}
+
+extern "C" int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                           const int32_t* block_expert, const int32_t* num_valid,
+                                           const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm,
+                                           int64_t tokens, const int32_t* row_rank, const int32_t* row_pair,
+                                           void* const* peer_slots, int world, int64_t peer_rows, int32_t* status,
+                                           void* stream) {
+  if (!row_rank || !row_pair || !peer_slots || world < 1 || world > 8 || peer_rows < 1 || !status) return B200MOE_E_ARG;
+  b200moe::EpilogueArgs ep{};
+  for (int r = 0; r < 8; ++r) {
+    ep.peer_slots[r] = static_cast<__nv_bfloat16*>(peer_slots[r < world ? r : 0]);
+    if (!ep.peer_slots[r] || (reinterpret_cast<uintptr_t>(ep.peer_slots[r]) & 15)) return B200MOE_E_ARG;
+  }
+  ep.row_rank = row_rank;
+  ep.row_pair = row_pair;
+  ep.world = world;
+  ep.peer_rows = peer_rows;
+  ep.status = status;
+  return gemm2_common(w2t, num_experts, hq, sfh, block_expert, num_valid, sorted_ids, sorted_w, max_rows, bm, tokens, ep,
+                      status, stream);
 }

@@ -275,6 +275,19 @@ def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):
     return slots
 
 
+def grouped_gemm2_peer(hq, sfh, sort: SortBuffers, w: MoeWeights, row_rank, row_pair, peer_ptrs, world: int,
+                       peer_rows: int):
+    """GEMM2 whose result rows go straight into the slot buffers of the ranks that own the pairs (expert parallel):
+    ``row_rank`` / ``row_pair`` int32 [4 * sort.tokens], ``peer_ptrs`` a ctypes array of ``world`` device pointers."""
+    dev = hq.device
+    _lib.check(_lib.load().b200moe_gemm2_weighted_peer(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
+                                                       _ptr(sort.block_expert), _ptr(sort.num_valid),
+                                                       _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), sort.max_rows,
+                                                       sort.bm, sort.tokens, _ptr(row_rank), _ptr(row_pair), peer_ptrs,
+                                                       world, peer_rows, _ptr(status_word(dev)), _stream(dev)),
+               "gemm2_weighted_peer")
+
+
 def simt_gemm1(x_quant, sort: SortBuffers, w: MoeWeights, rows=None):
     """The CUDA-core cross-check of ``grouped_gemm1`` on the checkpoint-layout weights (``keep_row_major=True``)."""
     if w.row_major is None:

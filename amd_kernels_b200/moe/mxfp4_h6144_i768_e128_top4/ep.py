@@ -83,21 +83,60 @@ def scatter_combined(returned: torch.Tensor, plan: DispatchPlan, tokens: int) ->
     return slots.view(tokens, TOPK, *returned.shape[1:])
 
 
+class PeerSlots:
+    """One bf16 [pairs, 6144] slot buffer per rank, each mapped into every other rank of the node, so GEMM2 on any rank
+    can store a result row where its owner will reduce it. The mapping comes from torch's symmetric memory (virtual-memory
+    handles mapped with access for the local device); the stores themselves are plain peer stores over NVLink."""
+
+    def __init__(self, max_pairs: int, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        world = dist.get_world_size(group)
+        self.max_pairs = max_pairs
+        if world == 1:  # nothing to map: the only slot buffer is local
+            self.local = torch.zeros((max_pairs, H), dtype=torch.bfloat16, device="cuda")
+            self.ptrs = (ctypes.c_void_p * 1)(self.local.data_ptr())
+            return
+        self.local = symm_mem.empty((max_pairs, H), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, group if group is not None else dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != world or ptrs[dist.get_rank(group)] != self.local.data_ptr():
+            raise RuntimeError("unexpected symmetric-memory layout")
+        self.ptrs = (ctypes.c_void_p * world)(*ptrs)
+        self.max_pairs = max_pairs
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+
 class ExpertParallelMoe:
     """One rank of the expert-parallel layer. ``weights`` holds this rank's experts only
     (``MoeWeights.from_row_major`` on the slice ``local_expert_ids(rank, world)`` of the checkpoint); routing parameters
     (bias over all 128 experts, mode, scale) describe the global router."""
 
     def __init__(self, weights, group=None, *, bias=None, routing_mode="softmax", scale=1.0, placement="contiguous",
-                 experts: int = E):
+                 experts: int = E, peer_pairs: int = 0):
+        """``peer_pairs`` > 0: fuse the combine into GEMM2 — result rows are stored straight into the owning rank's slot
+        buffer (room for ``peer_pairs`` = 4 x the largest local token count) instead of travelling back by all-to-all."""
         self.w, self.group = weights, group
+        self.peer = None
+        if peer_pairs:
+            ok = torch.ones(1, device="cuda")
+            try:
+                self.peer = PeerSlots(peer_pairs, group)
+            except Exception:  # no peer mapping on this machine: every rank falls back to the all-to-all combine
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if not bool(ok.item()):
+                self.peer = None
+            self._fence = torch.zeros(1, device="cuda")
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if experts % self.world or weights.num_experts != experts // self.world:
             raise ValueError(f"needs {experts // self.world} local experts on each of {self.world} ranks")
         self.bias, self.mode, self.scale, self.placement, self.experts = bias, routing_mode, float(scale), placement, experts
         self.last_recv_rows = 0
 
-    def experts_on_rows(self, codes, scales, local_expert, weight, n):
+    def experts_on_rows(self, codes, scales, local_expert, weight, n, row_rank=None, row_pair=None):
         """The grouped GEMMs on rows that arrived from any rank: row r < n -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r.
         The buffers hold a multiple of four rows (rows beyond n carry expert id -1 and are dropped by the sort)."""
         from . import chain
@@ -108,6 +147,10 @@ class ExpertParallelMoe:
         sort = chain.moe_sort(local_expert.view(groups, TOPK), weight.view(groups, TOPK), bm, self.w.num_experts)
         xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
         hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
+        if row_rank is not None:
+            chain.grouped_gemm2_peer(hq, sfh, sort, self.w, row_rank, row_pair, self.peer.ptrs, self.world,
+                                     self.peer.max_pairs)
+            return None
         slots = chain.grouped_gemm2(hq, sfh, sort, self.w)
         return slots.view(groups * TOPK, H)[:n]
 
@@ -129,7 +172,8 @@ class ExpertParallelMoe:
         padded = (n + TOPK - 1) // TOPK * TOPK
         self.last_recv_rows = n
         src_token = order // TOPK
-        meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32)], dim=1)
+        use_peer = self.peer is not None and tokens * TOPK <= self.peer.max_pairs
+        meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32), order.int()], dim=1)
 
         def exchange(rows, width, dtype, fill=None):
             out = torch.empty((padded, width), dtype=dtype, device=x.device)
@@ -141,8 +185,19 @@ class ExpertParallelMoe:
 
         r_codes = exchange(codes.index_select(0, src_token), H // 2, torch.uint8, 0)
         r_scales = exchange(scales.index_select(0, src_token), H // 32, torch.uint8, 0)
-        r_meta = exchange(meta, 2, torch.int32, -1)
-        y = self.experts_on_rows(r_codes, r_scales, r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32), n)
+        r_meta = exchange(meta, 3, torch.int32, -1)
+        r_expert, r_weight = r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32)
+        if use_peer:
+            # GEMM2 stores every result row into its owner's slot buffer; one tiny collective then orders the ranks
+            row_rank = torch.repeat_interleave(torch.arange(self.world, dtype=torch.int32, device=x.device),
+                                               torch.tensor(recv_counts, device=x.device), output_size=n)
+            if padded > n:
+                row_rank = torch.cat([row_rank, row_rank.new_zeros(padded - n)])
+            self.experts_on_rows(r_codes, r_scales, r_expert, r_weight, n, row_rank, r_meta[:, 2].contiguous())
+            dist.all_reduce(self._fence, group=self.group)
+            slots = self.peer.local[:tokens * TOPK].view(tokens, TOPK, H)
+            return slots.clone() if return_partials else chain.reduce_slots(slots)
+        y = self.experts_on_rows(r_codes, r_scales, r_expert, r_weight, n)
         back = torch.empty((tokens * TOPK, H), dtype=torch.bfloat16, device=x.device)
         dist.all_to_all_single(back, y.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts,
                                group=self.group)

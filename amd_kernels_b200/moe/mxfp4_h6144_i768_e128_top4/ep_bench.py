@@ -20,7 +20,7 @@ NVLINK_GBS_MEASURED = 770.0  # measured peer-copy bandwidth per direction per GP
 N_INPUTS = 4
 
 
-def build_rank_layer(rank, world, placement, seed=0):
+def build_rank_layer(rank, world, placement, seed=0, peer_pairs=0):
     from oracle import moe_oracle as orc
     from . import chain, ep
     (w13, s13, w2, s2), _ = orc.make_weights(seed=seed)
@@ -28,7 +28,8 @@ def build_rank_layer(rank, world, placement, seed=0):
     w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(np.ascontiguousarray(a[mine])).cuda()
                                                      for a in (w13, s13, w2, s2)))
     del w13, s13, w2, s2
-    return ep.ExpertParallelMoe(w, None, bias=None, routing_mode="softmax", scale=1.0, placement=placement)
+    return ep.ExpertParallelMoe(w, None, bias=None, routing_mode="softmax", scale=1.0, placement=placement,
+                                peer_pairs=peer_pairs)
 
 
 def run(args):
@@ -45,7 +46,7 @@ def run(args):
     t_loc = tokens_global // world
     zipf = bool(getattr(args, "zipf", False))
     placement = "interleaved" if zipf else "contiguous"
-    layer = build_rank_layer(rank, world, placement)
+    layer = build_rank_layer(rank, world, placement, peer_pairs=0 if os.environ.get("B200MOE_EP_COMBINE") == "nccl" else t_loc * TOPK)
     gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
     xs = [torch.randn((t_loc, H), device="cuda", generator=gen).bfloat16() for _ in range(N_INPUTS)]
     lgs = [torch.randn((t_loc, E), device="cuda", generator=gen) for _ in range(N_INPUTS)]
@@ -112,6 +113,8 @@ def run(args):
         t_fp4 = tokens_global / world * FLOPS_PER_TOKEN / (4 * peaks["bf16_tflops"] * 1e12)
         cfg = workload_config(tokens_global, world)
         cfg.update({"tokens_per_rank": t_loc, "expert_placement": placement, "routing_skew": "zipf 1.1" if zipf else "none",
+                    "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
+                    else "NCCL all-to-all of bf16 slot rows",
                     "max_rows_received_by_a_rank": max_rows, "mean_rows_received_per_rank": mean_rows,
                     "timing": "CUDA events per step on every rank after an untimed 512 MB L2 flush, max over ranks"})
         line = {"metric": "moe_layer_tokens_per_s", "value": tokens_global / (per_step * 1e-3), "unit": "tokens/s",

@@ -145,6 +145,20 @@ int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* h
                            const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
                            int32_t* status, void* stream);
 
+/* GEMM2 fused with the expert-parallel combine (no counterpart in the reference, which has no expert parallelism; its
+ * multi-GPU tail is MOE/prepared_input.py:189-209 + amd_kernels/collectives/pull_collectives_ranks4). Same computation as
+ * b200moe_gemm2_weighted, but result row of pair r (r = 4*token+slot of THIS rank's received rows) is stored straight
+ * into rank row_rank[r]'s slot buffer at pair row_pair[r]: peer_slots[k] is a device pointer to rank k's bf16 [pairs][6144]
+ * buffer of peer_rows rows (this rank's own buffer at index `rank`, the others peer mappings over NVLink); world <= 8.
+ * A rank or pair index outside those bounds is not stored and sets status = B200MOE_DEV_BAD_INDEX.
+ * Plain peer stores from the epilogue, no multicast, no waits. The caller orders the ranks afterwards (any collective on
+ * the same streams) before a rank reads its buffer. */
+int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                                const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, const int32_t* row_rank,
+                                const int32_t* row_pair, void* const* peer_slots, int world, int64_t peer_rows, int32_t* status,
+                                void* stream);
+
 /* Plain CUDA-core versions of the two grouped GEMMs on checkpoint-layout weights and row-major activations, same
  * outputs and output layouts as the tcgen05 kernels. They exist so the tensor-core kernels and the preshuffle can be
  * checked on the GPU at sizes the CPU oracle cannot reach; the product path never selects them. `rows`/`n_rows`: the

@@ -36,12 +36,15 @@ def _worker(rank, world, port, placement, errors):
         xb, lg = orc.make_inputs(gen, tokens, experts=experts)
         x = cu(xb.view(np.int16)).view(torch.bfloat16)
         logits = cu(lg)
-        par = ep.ExpertParallelMoe(w_local, None, routing_mode="softmax", scale=1.0, placement=placement, experts=experts)
-        for _ in range(2):
-            out = par.forward(x, logits)
-            ref = chain.mxfp4_moe(x, w_all, router_logits=logits)
-            torch.cuda.synchronize()
-            assert torch.equal(out, ref), "expert-parallel output differs from the single-GPU layer"
+        ref = chain.mxfp4_moe(x, w_all, router_logits=logits)
+        for peer_pairs in (0, 4 * 64):  # all-to-all combine, then the combine fused into GEMM2 over peer mappings
+            par = ep.ExpertParallelMoe(w_local, None, routing_mode="softmax", scale=1.0, placement=placement,
+                                       experts=experts, peer_pairs=peer_pairs)
+            assert peer_pairs == 0 or par.peer is not None, "peer mapping of the slot buffers failed"
+            for _ in range(2):
+                out = par.forward(x, logits)
+                torch.cuda.synchronize()
+                assert torch.equal(out, ref), f"expert-parallel output differs from the single-GPU layer ({peer_pairs})"
         assert chain.last_status() == 0
         dist.barrier()
         dist.destroy_process_group()
