@@ -119,7 +119,114 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
   }
 }
 
+// Expert-parallel dispatch fused with the quantisation: one CTA per send row quantises the pair's token row and stores
+// codes (3072 contiguous bytes), row-major scales (192 bytes) and a 16-byte meta record {expert id on the destination,
+// routing weight bits, source pair, source rank} straight into the destination rank's receive buffers (peer mappings over
+// NVLink, or local memory for rows that stay). Plain stores, no waits; the caller orders the ranks afterwards.
+struct PushArgs {
+  uint8_t* codes[8];
+  uint8_t* scales[8];
+  int32_t* meta[8];
+  int64_t dst_base[8];   // first row of this rank's segment in each destination's buffers
+  int32_t seg_start[8];  // first send row that goes to each destination
+  int32_t world, rank, experts_per_rank, interleaved;
+  int64_t capacity;      // rows every receive buffer holds
+};
+
+__global__ void __launch_bounds__(256) quant_push_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ ids,
+                                                         const int32_t* __restrict__ send_ids,
+                                                         const float* __restrict__ send_w,
+                                                         const int32_t* __restrict__ send_rank, int64_t tokens,
+                                                         PushArgs a, int32_t* status) {
+  constexpr int kIters = kH / 8 / 256;  // 3
+  const int lane = threadIdx.x & 31;
+  const int64_t i = blockIdx.x;
+  const int sid = send_ids[i];
+  const int64_t token = sid & 0x00ffffff;
+  const int slot = (sid >> 24) & 3, d = send_rank[i];
+  if (token >= tokens || d < 0 || d >= a.world) return;
+  const int64_t row = a.dst_base[d] + (i - a.seg_start[d]);
+  if (row < 0 || row >= a.capacity) {  // never store outside a receive buffer
+    if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
+    return;
+  }
+  const uint4* src = x + token * (kH / 8);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(a.codes[d] + row * (kH / 2));
+  uint32_t* sdst = reinterpret_cast<uint32_t*>(a.scales[d] + row * (kH / 32));
+  uint4 raw[kIters];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) raw[it] = src[it * 256 + threadIdx.x];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const uint32_t rr[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(rr[j] << 16);
+      v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const int e = quark_even_e8m0(amax);
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
+    dst[idx] = packed;
+    uint32_t sc = static_cast<uint32_t>(e);
+    sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
+    sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
+    if ((lane & 15) == 0) sdst[idx >> 4] = sc;  // scale bytes 4*(idx/16) .. +3 of the row
+  }
+  if (threadIdx.x == 0) {
+    const int e = ids[token * kTopK + slot];
+    const int local = a.interleaved ? e / a.world : e % a.experts_per_rank;
+    *reinterpret_cast<int4*>(a.meta[d] + row * 4) =
+        make_int4(local, __float_as_int(send_w[i]), static_cast<int>(token * kTopK + slot), a.rank);
+  }
+}
+
 }  // namespace b200moe
+
+extern "C" int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const int32_t* send_ids, const float* send_w,
+                                  const int32_t* send_rank, int64_t tokens, int world, int rank, int experts_per_rank,
+                                  int interleaved, void* const* peer_codes, void* const* peer_scales,
+                                  void* const* peer_meta, const int64_t* dst_base, const int32_t* seg_start,
+                                  int64_t capacity, int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!x_bf16 || !ids || !send_ids || !send_w || !send_rank || !peer_codes || !peer_scales || !peer_meta || !dst_base ||
+      !seg_start || !status)
+    return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || world < 1 || world > 8 || rank < 0 || rank >= world ||
+      experts_per_rank < 1 || capacity < 1)
+    return B200MOE_E_ARG;
+  PushArgs a{};
+  for (int r = 0; r < 8; ++r) {
+    const int k = r < world ? r : 0;
+    a.codes[r] = static_cast<uint8_t*>(peer_codes[k]);
+    a.scales[r] = static_cast<uint8_t*>(peer_scales[k]);
+    a.meta[r] = static_cast<int32_t*>(peer_meta[k]);
+    a.dst_base[r] = dst_base[k];
+    a.seg_start[r] = seg_start[k];
+    if (!a.codes[r] || !a.scales[r] || !a.meta[r]) return B200MOE_E_ARG;
+    if ((reinterpret_cast<uintptr_t>(a.codes[r]) | reinterpret_cast<uintptr_t>(a.scales[r]) |
+         reinterpret_cast<uintptr_t>(a.meta[r])) & 15)
+      return B200MOE_E_ALIGN;
+  }
+  a.world = world;
+  a.rank = rank;
+  a.experts_per_rank = experts_per_rank;
+  a.interleaved = interleaved;
+  a.capacity = capacity;
+  if (reinterpret_cast<uintptr_t>(x_bf16) & 15) return B200MOE_E_ALIGN;
+  B200MOE_LAUNCH_PLAIN(quant_push_kernel, static_cast<unsigned>(tokens * kTopK), 256, 0, static_cast<cudaStream_t>(stream),
+                       static_cast<const uint4*>(x_bf16), ids, send_ids, send_w, send_rank, tokens, a, status);
+  return 0;
+}
 
 extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, uint8_t* codes, uint8_t* scales,
                                    void* stream) {

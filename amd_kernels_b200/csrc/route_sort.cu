@@ -277,7 +277,8 @@ __global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restr
   place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, nullptr, sorted_ids, sorted_w, block_expert, num_valid);
 }
 
-static int shift_of(int bm) { return bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1; }
+// bm = 1 (no padding) serves the expert-parallel send order: pairs grouped by destination rank
+static int shift_of(int bm) { return bm == 1 ? 0 : bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1; }
 
 }  // namespace b200moe
 

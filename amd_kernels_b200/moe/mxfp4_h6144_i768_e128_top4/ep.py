@@ -83,30 +83,38 @@ def scatter_combined(returned: torch.Tensor, plan: DispatchPlan, tokens: int) ->
     return slots.view(tokens, TOPK, *returned.shape[1:])
 
 
-class PeerSlots:
-    """One bf16 [pairs, 6144] slot buffer per rank, each mapped into every other rank of the node, so GEMM2 on any rank
-    can store a result row where its owner will reduce it. The mapping comes from torch's symmetric memory (virtual-memory
-    handles mapped with access for the local device); the stores themselves are plain peer stores over NVLink."""
+class PeerBuffers:
+    """Buffers of one rank that every other rank of the node can store into (torch symmetric memory: virtual-memory
+    handles mapped with access for the local device; the stores themselves are plain peer stores over NVLink):
+    ``slots`` bf16 [pairs, 6144] where GEMM2 on any rank deposits this rank's result rows, and the receive buffers of
+    the dispatch (codes, row-major scales, meta) with room for every pair of every rank (the worst routing skew)."""
 
     def __init__(self, max_pairs: int, group=None):
         import ctypes
         import torch.distributed._symmetric_memory as symm_mem
-        world = dist.get_world_size(group)
-        self.max_pairs = max_pairs
-        if world == 1:  # nothing to map: the only slot buffer is local
-            self.local = torch.zeros((max_pairs, H), dtype=torch.bfloat16, device="cuda")
-            self.ptrs = (ctypes.c_void_p * 1)(self.local.data_ptr())
-            return
-        self.local = symm_mem.empty((max_pairs, H), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
-        self.local.zero_()
-        self.handle = symm_mem.rendezvous(self.local, group if group is not None else dist.group.WORLD)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        if len(ptrs) != world or ptrs[dist.get_rank(group)] != self.local.data_ptr():
-            raise RuntimeError("unexpected symmetric-memory layout")
-        self.ptrs = (ctypes.c_void_p * world)(*ptrs)
-        self.max_pairs = max_pairs
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_pairs, self.capacity = max_pairs, max_pairs * world
+        shapes = {"slots": ((max_pairs, H), torch.bfloat16), "codes": ((self.capacity, H // 2), torch.uint8),
+                  "scales": ((self.capacity, H // 32), torch.uint8), "meta": ((self.capacity, 4), torch.int32)}
+        self.local, self.ptrs, self._handles = {}, {}, []
+        dev = torch.device("cuda", torch.cuda.current_device())
+        for name, (shape, dtype) in shapes.items():
+            if world == 1:  # nothing to map
+                buf = torch.zeros(shape, dtype=dtype, device=dev)
+                ptrs = [buf.data_ptr()]
+            else:
+                buf = symm_mem.empty(shape, dtype=dtype, device=dev)
+                buf.zero_()
+                handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+                ptrs = [int(p) for p in handle.buffer_ptrs]
+                if len(ptrs) != world or ptrs[rank] != buf.data_ptr():
+                    raise RuntimeError("unexpected symmetric-memory layout")
+                self._handles.append(handle)
+            self.local[name] = buf
+            self.ptrs[name] = (ctypes.c_void_p * world)(*ptrs)
         torch.cuda.synchronize()
-        dist.barrier(group=group)
+        if world > 1:
+            dist.barrier(group=group)
 
 
 class ExpertParallelMoe:
@@ -123,7 +131,7 @@ class ExpertParallelMoe:
         if peer_pairs:
             ok = torch.ones(1, device="cuda")
             try:
-                self.peer = PeerSlots(peer_pairs, group)
+                self.peer = PeerBuffers(peer_pairs, group)
             except Exception:  # no peer mapping on this machine: every rank falls back to the all-to-all combine
                 ok.zero_()
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
@@ -148,7 +156,7 @@ class ExpertParallelMoe:
         xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
         hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
         if row_rank is not None:
-            chain.grouped_gemm2_peer(hq, sfh, sort, self.w, row_rank, row_pair, self.peer.ptrs, self.world,
+            chain.grouped_gemm2_peer(hq, sfh, sort, self.w, row_rank, row_pair, self.peer.ptrs["slots"], self.world,
                                      self.peer.max_pairs)
             return None
         slots = chain.grouped_gemm2(hq, sfh, sort, self.w)
@@ -160,6 +168,8 @@ class ExpertParallelMoe:
         tokens = x.shape[0]
         chain.variant_for(tokens)
         wt, ids = chain.topk_route(router_logits, self.bias, self.scale, self.mode)
+        if self.peer is not None and tokens * TOPK <= self.peer.max_pairs:
+            return self._forward_peer(x, wt, ids, return_partials)
         codes, scales = chain.mxfp4_quant(x)
         # where every pair goes; the row counts cross the ranks and reach the host in one read
         dest, local = expert_owner(ids.reshape(-1).long(), self.world, self.experts, self.placement)
@@ -172,8 +182,7 @@ class ExpertParallelMoe:
         padded = (n + TOPK - 1) // TOPK * TOPK
         self.last_recv_rows = n
         src_token = order // TOPK
-        use_peer = self.peer is not None and tokens * TOPK <= self.peer.max_pairs
-        meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32), order.int()], dim=1)
+        meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32)], dim=1)
 
         def exchange(rows, width, dtype, fill=None):
             out = torch.empty((padded, width), dtype=dtype, device=x.device)
@@ -185,18 +194,8 @@ class ExpertParallelMoe:
 
         r_codes = exchange(codes.index_select(0, src_token), H // 2, torch.uint8, 0)
         r_scales = exchange(scales.index_select(0, src_token), H // 32, torch.uint8, 0)
-        r_meta = exchange(meta, 3, torch.int32, -1)
+        r_meta = exchange(meta, 2, torch.int32, -1)
         r_expert, r_weight = r_meta[:, 0].contiguous(), r_meta[:, 1].contiguous().view(torch.float32)
-        if use_peer:
-            # GEMM2 stores every result row into its owner's slot buffer; one tiny collective then orders the ranks
-            row_rank = torch.repeat_interleave(torch.arange(self.world, dtype=torch.int32, device=x.device),
-                                               torch.tensor(recv_counts, device=x.device), output_size=n)
-            if padded > n:
-                row_rank = torch.cat([row_rank, row_rank.new_zeros(padded - n)])
-            self.experts_on_rows(r_codes, r_scales, r_expert, r_weight, n, row_rank, r_meta[:, 2].contiguous())
-            dist.all_reduce(self._fence, group=self.group)
-            slots = self.peer.local[:tokens * TOPK].view(tokens, TOPK, H)
-            return slots.clone() if return_partials else chain.reduce_slots(slots)
         y = self.experts_on_rows(r_codes, r_scales, r_expert, r_weight, n)
         back = torch.empty((tokens * TOPK, H), dtype=torch.bfloat16, device=x.device)
         dist.all_to_all_single(back, y.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts,
@@ -207,3 +206,46 @@ class ExpertParallelMoe:
         if return_partials:
             return back.index_select(0, where.long()).view(tokens, TOPK, H)
         return chain.reduce_rows(back, where, tokens)
+
+    def _forward_peer(self, x, wt, ids, return_partials):
+        """The fused form: (1) the pairs are grouped by destination rank by the routing-sort kernel; (2) one kernel
+        quantises every pair's row and stores it into the destination's receive buffers; (3) the grouped GEMMs run on
+        what arrived and GEMM2 stores every result row into its owner's slot buffer; (4) the owner reduces. Between the
+        phases one tiny all-reduce orders the ranks; the only host read is the W x W matrix of row counts."""
+        import ctypes
+        from . import chain
+        from ... import _lib
+        tokens, dev, peer = x.shape[0], x.device, self.peer
+        dest, _ = expert_owner(ids, self.world, self.experts, self.placement)
+        send = chain.moe_sort(dest.int().contiguous(), wt, 1, self.world)     # send order: pairs grouped by rank
+        counts = torch.bincount(dest.reshape(-1), minlength=self.world)
+        matrix = torch.empty((self.world, self.world), dtype=counts.dtype, device=dev)
+        dist.all_gather_into_tensor(matrix, counts, group=self.group)
+        m = matrix.tolist()                                                   # m[s][d] rows from rank s to rank d
+        seg_start, run = [], 0
+        for d in range(self.world):
+            seg_start.append(run)
+            run += m[self.rank][d]
+        dst_base = [sum(m[s][d] for s in range(self.rank)) for d in range(self.world)]
+        n = sum(m[s][self.rank] for s in range(self.world))
+        padded = (n + TOPK - 1) // TOPK * TOPK
+        self.last_recv_rows = n
+        base_arr = (ctypes.c_int64 * self.world)(*dst_base)
+        seg_arr = (ctypes.c_int32 * self.world)(*seg_start)
+        _lib.check(_lib.load().b200moe_quant_push(
+            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(send.sorted_ids.data_ptr()),
+            ctypes.c_void_p(send.sorted_weights.data_ptr()), ctypes.c_void_p(send.block_expert.data_ptr()), tokens,
+            self.world, self.rank, self.experts // self.world, int(self.placement == "interleaved"), peer.ptrs["codes"],
+            peer.ptrs["scales"], peer.ptrs["meta"], base_arr, seg_arr, peer.capacity,
+            ctypes.c_void_p(chain.status_word(dev).data_ptr()),
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "quant_push")
+        dist.all_reduce(self._fence, group=self.group)                        # every rank's rows have landed
+        meta = peer.local["meta"]
+        if padded > n:
+            meta[n:padded, 0] = -1                                            # rows beyond n are dropped by the sort
+        cols = meta[:padded].t().contiguous()                                 # expert, weight bits, source pair, source rank
+        self.experts_on_rows(peer.local["codes"][:padded], peer.local["scales"][:padded], cols[0],
+                             cols[1].view(torch.float32), n, cols[3], cols[2])
+        dist.all_reduce(self._fence, group=self.group)                        # every rank's result rows have landed
+        slots = peer.local["slots"][:tokens * TOPK].view(tokens, TOPK, H)
+        return slots.clone() if return_partials else chain.reduce_slots(slots)

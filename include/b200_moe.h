@@ -90,7 +90,8 @@ int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, uint8_t* code
 /* Routing sort (MOE/common/sort.py:19-65 SortBuffers; MOE/sort_a16w4.py:217-242 moe_sort_a16w4;
  * MOE/common/sort_count_all.py:188 moe_sort_count_all). ids/w [T][4] -> sorted_ids int32 [max_rows], sorted_w fp32
  * [max_rows], block_expert int32 [max_rows/bm], num_valid int32 [2] = {padded rows, first row of the last non-empty
- * expert}. `scratch` is int32 [ceil(4T/1024)][num_experts], needed only when 4T > 1024 (b200moe_permute_scratch_bytes). */
+ * expert}. `scratch` is int32 [ceil(4T/1024)][num_experts], needed only when 4T > 1024 (b200moe_permute_scratch_bytes).
+ * bm is 16, 32, 64 or 128; bm = 1 (no padding, block_expert = one entry per row) groups pairs by an arbitrary small key. */
 size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
 int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
                     float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
@@ -128,6 +129,19 @@ int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int
  * (the fused router + quant launches of the reference, MOE/router_topk_mxfp4_mxfp8_quant.py:35). */
 int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid, int64_t tokens,
                            int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, void* stream);
+
+/* Expert-parallel dispatch fused with the activation quantisation (no counterpart in the reference; its multi-GPU input
+ * hand-off is the all-gather of prepared inputs, MOE/prepared_input.py:116-209). send_ids / send_w / send_rank describe
+ * this rank's 4T pairs grouped by destination rank (b200moe_permute on the destination ranks with bm = 1: sorted_ids,
+ * sorted_w, block_expert). Send row i goes to row dst_base[d] + (i - seg_start[d]) of destination d's receive buffers:
+ * peer_codes[d] u8 [capacity][3072], peer_scales[d] u8 [capacity][192] (row-major, bit-identical to b200moe_quant_mxfp4
+ * of the token's row), peer_meta[d] int32 [capacity][4] = {expert id local to d, routing-weight bits, source pair
+ * 4*token+slot, source rank}. Pointers are device pointers valid on this GPU (peer mappings over NVLink; this rank's own
+ * buffers at index `rank`); world <= 8. Rows outside [0, capacity) are not stored and set status = B200MOE_DEV_BAD_INDEX. */
+int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const int32_t* send_ids, const float* send_w,
+                       const int32_t* send_rank, int64_t tokens, int world, int rank, int experts_per_rank,
+                       int interleaved, void* const* peer_codes, void* const* peer_scales, void* const* peer_meta,
+                       const int64_t* dst_base, const int32_t* seg_start, int64_t capacity, int32_t* status, void* stream);
 
 /* Grouped GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 block-scaled FP4 MMA
  * (MOE/gemm1_prefill_h6144_i768.py:71-898, MOE/gemm1_a4w4_small.py:75-164; oracle MOE/reference.py:66-72).
