@@ -296,3 +296,27 @@ def test_expert_parallel_path_equals_the_layer_bit_for_bit(C, layer, tokens):
     assert torch.equal(fused.forward(x, logits, return_partials=True), ref_slots)
     torch.cuda.synchronize()
     assert C.last_status() == 0
+
+
+def test_largest_sizes_cross_int32_byte_offsets(C, layer):
+    """65536 and 87381 tokens (the slot tensor is 3.2 / 4.3 GB: byte offsets exceed int32, as in the reference's
+    tests/moe/.../test_gemm_half_rows.py:28-30): the last tokens of the big batch equal, bit for bit, the same tokens run
+    as a batch of 16; outputs are finite; the reduce identity holds on the tail."""
+    raw, w, _, _ = layer
+    for tokens in (65536, 87381):
+        gen = torch.Generator(device="cuda").manual_seed(tokens)
+        x = torch.randn((tokens, H), device="cuda", generator=gen).bfloat16()
+        logits = torch.randn((tokens, 128), device="cuda", generator=gen)
+        slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
+        tail = slice(tokens - 16, tokens)
+        small, _ = C.mxfp4_moe(x[tail].contiguous(), w, router_logits=logits[tail].contiguous(), return_partials=True)
+        torch.cuda.synchronize()
+        assert C.last_status() == 0
+        assert torch.equal(slots[tail], small)
+        assert bool(torch.isfinite(slots[::997].float()).all())
+        out = C.mxfp4_moe(x, w, router_logits=logits)
+        assert np.array_equal(bits_of(out[tail]), orc.reduce_slots_bf16(bits_of(slots[tail])))
+        del slots, out, x, logits
+        torch.cuda.empty_cache()
+    with pytest.raises(ValueError):
+        C.mxfp4_moe(torch.zeros((87382, H), device="cuda", dtype=torch.bfloat16), w, router_logits=torch.zeros((87382, 128), device="cuda"))
