@@ -37,7 +37,8 @@ SIGNATURES = {
     "b200moe_permute_static": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P]),
     "b200moe_route_sort": (c_int, [_P, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P, _P, _P]),
-    "b200moe_quant_dispatch": (c_int, [_P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
+    "b200moe_quant_dispatch": (c_int, [_P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, _P]),
+    "b200moe_gemm12": (c_int, [_P, _P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, _P, _P, _P]),
     "b200moe_quant_push": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int64,
                                    _P, _P]),
     "b200moe_gemm1_swiglu_quant": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, c_int, _P, _P, _P, _P]),

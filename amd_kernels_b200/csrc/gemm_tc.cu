@@ -7,6 +7,7 @@
 //
 //   warp 0    producer: one thread issues TMA tile loads (128B-swizzled FP4 tiles) and bulk copies of scale atoms
 //   warp 1    MMA: allocates TMEM; one thread copies scale atoms to TMEM (tcgen05.cp) and issues tcgen05.mma
+//   (the one-launch kernel gemm12_kernel adds warp 6: a second producer for the token-side operand)
 //   warps 2-5 epilogue (bm = 128: a second group, warps 6-9, takes every other unit): tcgen05.ld of the accumulator, then
 //             GEMM1: SwiGLU-OAI (gate and up rows of one tile live in neighbouring lane quarters), MXFP4 requantisation
 //                    of 32 intermediate columns = the 32 lanes of a warp, codes and scale atoms to global memory
@@ -553,6 +554,334 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   }
 }
 
+// ------------------------------------------------------------------------------------------------ GEMM1 + GEMM2 in one launch
+// Decode sizes (bm < 128): both grouped GEMMs as ONE persistent kernel. The unit list is all GEMM1 units followed by all
+// GEMM2 units, dealt round-robin to the CTAs, so every CTA finishes its GEMM1 units before its first GEMM2 unit. A GEMM2
+// unit of row block b needs the 12 GEMM1 tiles of b: each GEMM1 epilogue publishes its stores (fence, then one atomic
+// add on done[b]) and the GEMM2 producer waits -- bounded like every other wait -- until done[b] == 12 before it loads h.
+// GEMM1 units never wait, so progress does not depend on scheduling order. What this buys over two launches: no ramp
+// between the kernels, and the short GEMM2 units (52 KB of weights) fill the uneven last round of GEMM1 (418 KB units).
+template <int BM>
+struct Cfg12 {
+  using C1 = Cfg<1, BM>;
+  static constexpr int kStageBytes = C1::kStageBytes;
+  static constexpr int kStages = BM == 64 ? 6 : 8;
+  static constexpr int kEpi1 = Cfg<1, BM>::kEpiBytes, kEpi2 = Cfg<2, BM>::kEpiBytes;
+  static constexpr int kEpiBytes = kEpi1 > kEpi2 ? kEpi1 : kEpi2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;
+};
+
+__device__ __forceinline__ bool wait_count(const int32_t* counter, int target, volatile int* abort_flag, int32_t* status) {
+  const uint64_t t0 = global_timer();
+  uint32_t spins = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= target) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicExch(status, B200MOE_DEV_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+template <int BM>
+__global__ void __launch_bounds__(224, 1)
+    gemm12_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_h,
+                  const uint8_t* __restrict__ w13t, const uint8_t* __restrict__ w2t, const uint8_t* __restrict__ sf_x,
+                  const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid, EpilogueArgs ep,
+                  int32_t* done, int32_t* status, int num_experts, int max_blocks) {
+  using C = Cfg<1, BM>;  // stage layout, TMEM columns and epilogue geometry are those of the swap orientation
+  using C2 = Cfg<2, BM>;
+  using CC = Cfg12<BM>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[CC::kStages];
+  __shared__ __align__(8) uint64_t bar_empty[CC::kStages];
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ __nv_bfloat16* s_dst[BM];
+  __shared__ float s_wt[BM];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abort_v = &abort_flag;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < CC::kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_tfull[a]), 1);
+      mbar_init(smem_u32(&bar_tempty[a]), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  pdl_wait();
+  launder(w13t);
+  launder(w2t);
+  launder(sf_x);
+  launder(block_expert);
+  launder(num_valid);
+  launder(ep.sorted_ids);
+  launder(ep.sorted_w);
+  int n_blocks = __ldcg(num_valid) / BM;
+  if (n_blocks < 0 || n_blocks > max_blocks) {
+    if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
+    n_blocks = 0;
+  }
+  const int units1 = n_blocks * kW13Tiles;
+  const int total_units = units1 + n_blocks * kW2Tiles;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- weight producer: arms each stage, streams tile records
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const bool second = u >= units1;
+        const int v = second ? u - units1 : u;
+        const int tiles_m = second ? kW2Tiles : kW13Tiles, tiles_k = second ? kK2Tiles : kK1Tiles;
+        const int b = v / tiles_m, mt = v % tiles_m;
+        int e = __ldcg(block_expert + b);
+        if (e < 0 || e >= num_experts) {
+          atomicExch(status, B200MOE_DEV_BAD_INDEX);
+          e = 0;
+        }
+        const uint8_t* w_src = (second ? w2t : w13t) + static_cast<int64_t>(e * tiles_m + mt) * tiles_k * kTileRecordBytes;
+        for (int kt = 0; kt < tiles_k; ++kt, ++it) {
+          const uint32_t s = it % CC::kStages, ph = (it / CC::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_arrive_expect_tx(full, C::kStageBytes);  // the whole stage: the activation producer's bytes included
+          bulk_load(tiles + s * C::kStageBytes, w_src + static_cast<int64_t>(kt) * kTileRecordBytes, kTileRecordBytes, full);
+        }
+      }
+      if (!ok) {
+        const uint32_t pending = it < CC::kStages ? it : CC::kStages;
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t idx = it - 1 - j, s = idx % CC::kStages, ph = (idx / CC::kStages) & 1u;
+          const uint64_t t0 = global_timer();
+          while (!mbar_try_wait(smem_u32(&bar_full[s]), ph) && global_timer() - t0 < kWaitLimitNs) {}
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- activation producer: token codes and their scales.
+    // Its own thread, because the fences a GEMM2 unit needs (acquire, then generic -> async proxy) must not sit in the
+    // thread that keeps the weight stream full.
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true, have_next = false;
+      int next_count = 0;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const bool second = u >= units1;
+        const int v = second ? u - units1 : u;
+        const int tiles_m = second ? kW2Tiles : kW13Tiles, tiles_k = second ? kK2Tiles : kK1Tiles;
+        const int b = v / tiles_m;
+        const uint8_t* sfb_src = second ? ep.sfh + static_cast<int64_t>(b) * C2::kActAtomsPerBlock * kAtomBytes
+                                        : sf_x + static_cast<int64_t>(b) * C::kActAtomsPerBlock * kAtomBytes;
+        if (second) {
+          // h of this row block must be complete and visible to the copy engine before it is read. The count was
+          // fetched while the previous unit's copies were issued, so the usual case costs no memory round trip.
+          // Usual case: the count is already 12. The writers ordered their stores for the copy engine before they
+          // counted (see the GEMM1 epilogue) and the copy below cannot issue before this branch has seen the count,
+          // so no fence is needed here; fences in this thread would wait for its own copies in flight.
+          if (!(have_next && next_count >= kW13Tiles)) {
+            if (!wait_count(done + b, kW13Tiles, abort_v, status)) { ok = false; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
+        for (int kt = 0; kt < tiles_k; ++kt, ++it) {
+          const uint32_t s = it % CC::kStages, ph = (it / CC::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t base = tiles + s * C::kStageBytes;
+          tma_load_2d(base + C::kBOffset, second ? &map_h : &map_x, kt * 128, b * BM, full);
+          bulk_load(base + C::kSfbOffset, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
+        }
+        const int un = u + static_cast<int>(gridDim.x);  // look ahead: the next unit's completion count
+        have_next = un < total_units && un >= units1;
+        if (have_next)
+          asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(next_count) : "l"(done + (un - units1) / kW2Tiles) : "memory");
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BM >> 3) << 17) | (1u << 23) | (8u << 24);
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+        const int tiles_k = u >= units1 ? kK2Tiles : kK1Tiles;
+        const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
+        for (int kt = 0; kt < tiles_k; ++kt, ++it) {
+          const uint32_t s = it % CC::kStages, ph = (it / CC::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t base = tiles + s * C::kStageBytes;
+          const uint32_t sfa = base + C::kABytes, sfb = base + C::kSfbOffset;
+          tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(sfa));
+          tc_cp_scales(tmem_base + C::kSfaCol + 4, scale_desc(sfa + kAtomBytes));
+          tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(sfb));
+          tc_cp_scales(tmem_base + C::kSfbCol + 4, scale_desc(sfb + kAtomBytes));
+          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t sf_id = (k & 1) * 2u;
+            const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
+            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
+                        tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
+          }
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + CC::kStages * C::kStageBytes);
+    uint32_t ui = 0;
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
+      const bool second = u >= units1;
+      const int v = second ? u - units1 : u;
+      const int tiles_m = second ? kW2Tiles : kW13Tiles;
+      const int b = v / tiles_m, mt = v % tiles_m;
+      const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+      const int64_t row0 = static_cast<int64_t>(b) * BM;
+      if (second && et < BM) {
+        s_dst[et] = slot_row(ep, __ldcg(ep.sorted_ids + row0 + et));
+        s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
+      }
+      if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status), 1u)) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
+      if (!second) {
+        float* mine = stage_f + (q >> 1) * 68 + (q & 1) * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BM; c0 += C::kEpiCols) {
+#pragma unroll 1
+          for (int cc = 0; cc < C::kEpiCols; cc += 16) {
+            uint32_t vv[16];
+            tc_ld16(t_acc + c0 + cc, vv);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mine[(cc + j) * C::kEpiRowFloats] = __uint_as_float(vv[j]);
+          }
+          if (c0 + C::kEpiCols >= BM) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int item = et; item < 2 * C::kEpiCols; item += 128) {
+            const int j = item >> 1, g = item & 1;
+            const float4* src = reinterpret_cast<const float4*>(stage_f + j * C::kEpiRowFloats + g * 68);
+            float h[32];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float4 gv = src[k], uv = src[8 + k];
+              h[4 * k + 0] = swiglu_oai(gv.x, uv.x);
+              h[4 * k + 1] = swiglu_oai(gv.y, uv.y);
+              h[4 * k + 2] = swiglu_oai(gv.z, uv.z);
+              h[4 * k + 3] = swiglu_oai(gv.w, uv.w);
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) amax = fmaxf(amax, fabsf(h[k]));
+            const int sc = quark_even_e8m0(amax);
+            const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
+            uint32_t words[4];
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd) {
+              uint32_t acc_w = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
+              words[wd] = acc_w;
+            }
+            const int grp = 2 * mt + g;
+            const int n = c0 + j;
+            *reinterpret_cast<uint4*>(ep.hq + (row0 + n) * (kI / 2) + grp * 16) =
+                make_uint4(words[0], words[1], words[2], words[3]);
+            ep.sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(n, grp & 3)] =
+                static_cast<uint8_t>(sc);
+          }
+          // this thread's h stores: ordered for the copy engine (async proxy) and visible device-wide before the count moves
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (et == 0) atomicAdd(done + b, 1);  // one more GEMM1 tile of row block b is complete
+      } else {
+        float* mine = stage_f + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BM; c0 += C2::kOutCols) {
+#pragma unroll
+          for (int cc = 0; cc < C2::kOutCols; cc += 16) {
+            uint32_t vv[16];
+            tc_ld16(t_acc + c0 + cc, vv);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mine[(cc + j) * C2::kOutRowFloats] = __uint_as_float(vv[j]);
+          }
+          if (c0 + C2::kOutCols >= BM) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 2
+          for (int item = et; item < C2::kOutCols * 32; item += 128) {
+            const int j = item >> 5, seg = item & 31;
+            __nv_bfloat16* row_dst = s_dst[c0 + j];
+            if (row_dst != nullptr) {
+              const float s_w = s_wt[c0 + j];
+              const float4 x4 = *reinterpret_cast<const float4*>(stage_f + j * C2::kOutRowFloats + seg * 4);
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(x4.x * s_w, x4.y * s_w);
+              const __nv_bfloat162 hi = __floats2bfloat162_rn(x4.z * s_w, x4.w * s_w);
+              uint2 packed;
+              packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+              packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(row_dst + mt * 128 + seg * 4) = packed;
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -628,7 +957,62 @@ static int launch_bm(int bm, const CUtensorMap& mx, const uint8_t* w_tiles, cons
 
 static bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
+template <int BM>
+static int launch12(const CUtensorMap& mx, const CUtensorMap& mh, const uint8_t* w13t, const uint8_t* w2t,
+                    const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep,
+                    int32_t* done, int64_t max_rows, int num_experts, int32_t* status, cudaStream_t stream) {
+  using CC = Cfg12<BM>;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm12_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, CC::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int64_t max_units = max_rows / BM * (kW13Tiles + kW2Tiles);
+  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  if (grid <= 0) return 0;
+  B200MOE_LAUNCH((gemm12_kernel<BM>), grid, 224, CC::kSmemBytes, stream, mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep,
+                 done, status, num_experts, static_cast<int>(max_rows / BM));
+  return 0;
+}
+
 }  // namespace b200moe
+
+extern "C" int b200moe_gemm12(const uint8_t* w13t, const uint8_t* w2t, int num_experts, const uint8_t* xq_sorted,
+                              const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
+                              const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm, int64_t tokens,
+                              uint8_t* hq, uint8_t* sfh, int32_t* done, void* slots_bf16, int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w13t || !w2t || !xq_sorted || !sfx || !block_expert || !num_valid || !sorted_ids || !sorted_w || !hq || !sfh ||
+      !done || !slots_bf16 || !status)
+    return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || tokens < 0 || (bm != 16 && bm != 32 && bm != 64) ||
+      max_rows % bm)
+    return B200MOE_E_ARG;
+  if (misaligned(w13t, 16) || misaligned(w2t, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) ||
+      misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  CUtensorMap mx, mh;
+  int r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  if (r) return r;
+  r = make_map(&mh, hq, kI / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));
+  if (r) return r;
+  EpilogueArgs ep{};
+  ep.hq = hq;
+  ep.sfh = sfh;
+  ep.sorted_ids = sorted_ids;
+  ep.sorted_w = sorted_w;
+  ep.slots = static_cast<__nv_bfloat16*>(slots_bf16);
+  ep.tokens = tokens;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (bm) {
+    case 16: return launch12<16>(mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep, done, max_rows, num_experts, status, st);
+    case 32: return launch12<32>(mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep, done, max_rows, num_experts, status, st);
+    case 64: return launch12<64>(mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep, done, max_rows, num_experts, status, st);
+  }
+  return B200MOE_E_ARG;
+}
 
 extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted,
                                           const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,

@@ -67,9 +67,14 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
                                                              const int32_t* __restrict__ sorted_ids,
                                                              const int32_t* __restrict__ num_valid, int64_t tokens,
                                                              int bm_shift, uint8_t* __restrict__ xq_sorted,
-                                                             uint8_t* __restrict__ sfx) {
+                                                             uint8_t* __restrict__ sfx, int32_t* __restrict__ done,
+                                                             int n_done) {
   pdl_enter(x, sorted_ids, num_valid);
   constexpr int kIters = kH / 8 / 256;  // 3
+  {  // the per-block completion counts of the one-launch GEMM1+GEMM2 start every call at zero
+    const int64_t z = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (done != nullptr && z < n_done) done[z] = 0;
+  }
   const int lane = threadIdx.x & 31;
   const int64_t row = blockIdx.x;
   if (row >= __ldcg(num_valid)) return;
@@ -258,7 +263,7 @@ extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales
 
 extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid,
                                       int64_t tokens, int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
-                                      void* stream) {
+                                      int32_t* done, void* stream) {
   using namespace b200moe;
   if (!x_bf16 || !sorted_ids || !num_valid || !xq_sorted || !sfx || tokens < 0 || max_rows < 0) return B200MOE_E_ARG;
   const int shift = bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1;
@@ -268,6 +273,6 @@ extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
   const unsigned grid = static_cast<unsigned>(max_rows);
-  B200MOE_LAUNCH(quant_dispatch_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx);
+  B200MOE_LAUNCH(quant_dispatch_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), sorted_ids, num_valid, tokens, shift, xq_sorted, sfx, done, static_cast<int>(max_rows / bm));
   return 0;
 }

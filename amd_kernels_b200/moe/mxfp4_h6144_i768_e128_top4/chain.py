@@ -223,7 +223,7 @@ def quant_dispatch(x: torch.Tensor, sort: SortBuffers):
     xq = torch.empty((sort.max_rows, H // 2), dtype=torch.uint8, device=dev)
     sfx = torch.empty((sort.max_rows // sort.bm, H // 128, 512), dtype=torch.uint8, device=dev)
     _lib.check(_lib.load().b200moe_quant_dispatch(_ptr(x), _ptr(sort.sorted_ids), _ptr(sort.num_valid), sort.tokens,
-                                                  sort.bm, sort.max_rows, _ptr(xq), _ptr(sfx), _stream(dev)),
+                                                  sort.bm, sort.max_rows, _ptr(xq), _ptr(sfx), None, _stream(dev)),
                "quant_dispatch")
     return xq, sfx
 
@@ -261,6 +261,23 @@ def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
                                                       sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
                                                       _ptr(status_word(dev)), _stream(dev)), "gemm1_swiglu_quant")
     return hq, sfh
+
+
+def grouped_gemm12(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, slots=None):
+    """Both grouped GEMMs in one persistent launch (block heights 16 / 32 / 64): -> (slots, h codes, h scale atoms), the
+    same bits as ``grouped_gemm1`` followed by ``grouped_gemm2`` (reference gemm12_a4w4.py:24)."""
+    dev = xq_sorted.device
+    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
+    done = torch.zeros(sort.max_rows // sort.bm, dtype=torch.int32, device=dev)
+    if slots is None:
+        slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.load().b200moe_gemm12(_ptr(w.w13), _ptr(w.w2), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
+                                          _ptr(sort.block_expert), _ptr(sort.num_valid), _ptr(sort.sorted_ids),
+                                          _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens, _ptr(hq),
+                                          _ptr(sfh), _ptr(done), _ptr(slots), _ptr(status_word(dev)), _stream(dev)),
+               "gemm12")
+    return slots, hq, sfh
 
 
 def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):

@@ -126,9 +126,10 @@ int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int
 
 /* Quantisation fused with the gather: bf16 x [T][6144] -> xq_sorted / sfx as above, same bits as b200moe_quant_mxfp4
  * followed by b200moe_dispatch_rows except that padding rows get the scale byte of an all-zero block (1)
- * (the fused router + quant launches of the reference, MOE/router_topk_mxfp4_mxfp8_quant.py:35). */
+ * (the fused router + quant launches of the reference, MOE/router_topk_mxfp4_mxfp8_quant.py:35). `done` (may be null):
+ * int32 [max_rows/bm], zeroed by this kernel for a following b200moe_gemm12. */
 int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid, int64_t tokens,
-                           int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, void* stream);
+                           int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, int32_t* done, void* stream);
 
 /* Expert-parallel dispatch fused with the activation quantisation (no counterpart in the reference; its multi-GPU input
  * hand-off is the all-gather of prepared inputs, MOE/prepared_input.py:116-209). send_ids / send_w / send_rank describe
@@ -158,6 +159,17 @@ int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const uint8_t* h
                            const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
                            const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, void* slots_bf16,
                            int32_t* status, void* stream);
+
+/* Both grouped GEMMs in ONE persistent launch, for bm = 16 / 32 / 64 (MOE/gemm12_a4w4.py:24 gemm12_a4w4: GEMM1 and GEMM2
+ * work in one launch ordered by ready counters). Same inputs, outputs and bits as b200moe_gemm1_swiglu_quant followed by
+ * b200moe_gemm2_weighted. `done` int32 [max_rows/bm] must be zero on entry (b200moe_quant_dispatch zeroes it); it counts
+ * the finished GEMM1 tiles of every row block, and a GEMM2 unit starts when its block shows 12. Unlike the reference's
+ * wait, the wait here is bounded (about two seconds, then status = B200MOE_DEV_TIMEOUT and the kernel winds down), and
+ * GEMM1 work never waits, so completion does not depend on the order in which CTAs are scheduled. */
+int b200moe_gemm12(const uint8_t* w13t, const uint8_t* w2t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
+                   const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids, const float* sorted_w,
+                   int64_t max_rows, int bm, int64_t tokens, uint8_t* hq, uint8_t* sfh, int32_t* done, void* slots_bf16,
+                   int32_t* status, void* stream);
 
 /* GEMM2 fused with the expert-parallel combine (no counterpart in the reference, which has no expert parallelism; its
  * multi-GPU tail is MOE/prepared_input.py:189-209 + amd_kernels/collectives/pull_collectives_ranks4). Same computation as

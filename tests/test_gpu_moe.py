@@ -320,3 +320,27 @@ def test_largest_sizes_cross_int32_byte_offsets(C, layer):
         torch.cuda.empty_cache()
     with pytest.raises(ValueError):
         C.mxfp4_moe(torch.zeros((87382, H), device="cuda", dtype=torch.bfloat16), w, router_logits=torch.zeros((87382, 128), device="cuda"))
+
+
+@pytest.mark.parametrize("tokens,bm,kind", [(1, 16, "uniform"), (16, 16, "uniform"), (100, 32, "hot"), (256, 32, "uniform"),
+                                            (700, 64, "uniform"), (300, 16, "one")])
+def test_one_launch_gemm12_equals_two_launches(C, layer, tokens, bm, kind):
+    """GEMM1 and GEMM2 in one persistent launch (the decode path of the entry) against the two separate launches: h codes,
+    h scales and slots bit for bit (the reference's tests/moe/.../test_gemm12_a4w4.py:65-77), three runs in a row."""
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(500 + tokens)
+    xb, _ = orc.make_inputs(gen, tokens)
+    ids, wts = make_routing(tokens, kind, seed=tokens)
+    x = bf16_dev(xb)
+    sb = C.moe_sort(dev(ids), dev(wts), bm)
+    xq, sfx = C.quant_dispatch(x, sb)
+    hq, sfh = C.grouped_gemm1(xq, sfx, sb, w)
+    ref = C.grouped_gemm2(hq, sfh, sb, w, slots=torch.zeros((tokens, 4, H), dtype=torch.bfloat16, device="cuda"))
+    nv = int(sb.num_valid[0])
+    for _ in range(3):
+        slots, hq2, sfh2 = C.grouped_gemm12(xq, sfx, sb, w, slots=torch.zeros((tokens, 4, H), dtype=torch.bfloat16, device="cuda"))
+        torch.cuda.synchronize()
+        assert C.last_status() == 0
+        assert torch.equal(hq2[:nv], hq[:nv])
+        assert np.array_equal(atoms_to_rowmajor(sfh2.cpu().numpy(), bm)[:nv], atoms_to_rowmajor(sfh.cpu().numpy(), bm)[:nv])
+        assert torch.equal(slots, ref)
