@@ -197,21 +197,53 @@ struct EpilogueArgs {
   int32_t* status;
 };
 
-// Where the result row of sorted-row entry `sid` goes (null: a padding row).
-__device__ __forceinline__ __nv_bfloat16* slot_row(const EpilogueArgs& ep, int sid) {
-  const int64_t token = sid & 0x00ffffff;
-  if (token >= ep.tokens) return nullptr;
-  const int64_t pair = token * kTopK + ((sid >> 24) & 3);
-  if (ep.row_rank == nullptr) return ep.slots + pair * kH;
-  const int rank = __ldcg(ep.row_rank + pair);
-  const int64_t dst_pair = __ldcg(ep.row_pair + pair);
-  if (rank < 0 || rank >= ep.world || dst_pair < 0 || dst_pair >= ep.peer_rows) {  // never store through a bad index
-    atomicExch(ep.status, B200MOE_DEV_BAD_INDEX);
-    return nullptr;
+// What the GEMM2 epilogue needs to place a result row, held in registers / shared memory (never indexed dynamically
+// inside the kernel-parameter struct, which would push the whole struct into local memory).
+struct RowPlacer {
+  __nv_bfloat16* slots;
+  int64_t tokens;
+  const int32_t* row_rank;
+  const int32_t* row_pair;
+  __nv_bfloat16* const* peers;  // shared-memory copy of the peer table
+  int world;
+  int64_t peer_rows;
+  int32_t* status;
+  // Where the result row of sorted-row entry `sid` goes (null: a padding row).
+  __device__ __forceinline__ __nv_bfloat16* row(int sid) const {
+    const int64_t token = sid & 0x00ffffff;
+    if (token >= tokens) return nullptr;
+    const int64_t pair = token * kTopK + ((sid >> 24) & 3);
+    if (row_rank == nullptr) return slots + pair * kH;
+    const int rank = __ldcg(row_rank + pair);
+    const int64_t dst_pair = __ldcg(row_pair + pair);
+    if (rank < 0 || rank >= world || dst_pair < 0 || dst_pair >= peer_rows) {  // never store through a bad index
+      atomicExch(status, B200MOE_DEV_BAD_INDEX);
+      return nullptr;
+    }
+    return peers[rank] + dst_pair * kH;
   }
-  return ep.peer_slots[rank] + dst_pair * kH;
-}
+};
 
+// Copies the fields of the kernel parameter into registers (laundered: they point at data a predecessor kernel wrote)
+// and the peer table into shared memory. Call after pdl_wait(), before the roles split; `s_peer` is a __shared__ array.
+__device__ __forceinline__ RowPlacer make_placer(const EpilogueArgs& ep, __nv_bfloat16** s_peer) {
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s_peer[r] = ep.peer_slots[r];
+  }
+  RowPlacer p;
+  p.slots = ep.slots;
+  p.tokens = ep.tokens;
+  p.row_rank = ep.row_rank;
+  p.row_pair = ep.row_pair;
+  p.peers = s_peer;
+  p.world = ep.world;
+  p.peer_rows = ep.peer_rows;
+  p.status = ep.status;
+  launder(p.row_rank);
+  launder(p.row_pair);
+  return p;
+}
 
 template <int MODE, int BM>
 __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
@@ -228,6 +260,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ __nv_bfloat16* s_dst[MODE == 2 ? BM : 1];
+  __shared__ __nv_bfloat16* s_peer[8];
   __shared__ float s_wt[MODE == 2 ? BM : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,10 +298,12 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   launder(sf_x);
   launder(block_expert);
   launder(num_valid);
-  launder(ep.sorted_ids);
-  launder(ep.sorted_w);
-  launder(ep.row_rank);
-  launder(ep.row_pair);
+  const int32_t* sorted_ids = ep.sorted_ids;
+  const float* sorted_w = ep.sorted_w;
+  launder(sorted_ids);
+  launder(sorted_w);
+  const RowPlacer placer = make_placer(ep, s_peer);
+  __syncthreads();
   int n_blocks = __ldcg(num_valid) / BM;
   if (n_blocks < 0 || n_blocks > max_blocks) {  // a routing table that does not fit its buffers: record it, do nothing
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
@@ -358,6 +393,9 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     const int tr = q * 32 + lane;     // the TMEM lane this thread reads (warps 2..5 own quarters 2, 3, 0, 1)
     float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + C::kStages * C::kStageBytes);
     uint32_t ui = 0;
+    bool have_ahead = false;
+    int ahead_sid = 0;
+    float ahead_wt = 0.0f;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       if (C::kEpiGroups == 2 && static_cast<int>(ui & 1u) != group) continue;  // group g owns accumulator buffer g
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
@@ -366,15 +404,29 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
       __nv_bfloat16* my_dst = nullptr;
       float my_wt = 0.0f;
       if (MODE == 2 && C::kTokensAreM) {  // one token row per thread; fetched before the wait, hidden behind the MMAs
-        my_dst = slot_row(ep, __ldcg(ep.sorted_ids + row0 + tr));
-        my_wt = __ldcg(ep.sorted_w + row0 + tr);
+        my_dst = placer.row(__ldcg(sorted_ids + row0 + tr));
+        my_wt = __ldcg(sorted_w + row0 + tr);
       } else if (MODE == 2 && et < BM) {
-        s_dst[et] = slot_row(ep, __ldcg(ep.sorted_ids + row0 + et));
-        s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
+        // this block's rows; normally fetched one unit ahead (below), so no memory round trip sits in front of the wait
+        if (!have_ahead) {
+          ahead_sid = __ldcg(sorted_ids + row0 + et);
+          ahead_wt = __ldcg(sorted_w + row0 + et);
+        }
+        s_dst[et] = placer.row(ahead_sid);
+        s_wt[et] = ahead_wt;
       }
       // the four warps must agree before they meet at the named barrier below
       if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status), 1u + group)) break;
       tc_fence_after();
+      if (MODE == 2 && !C::kTokensAreM) {  // look ahead: the rows of this CTA's next unit
+        const int un = u + static_cast<int>(gridDim.x);
+        have_ahead = un < total_units;
+        if (have_ahead && et < BM) {
+          const int64_t r1 = static_cast<int64_t>(un / C::kTilesM) * BM + et;
+          ahead_sid = __ldcg(sorted_ids + r1);
+          ahead_wt = __ldcg(sorted_w + r1);
+        }
+      }
       const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       if (C::kTokensAreM && MODE == 1) {
         // lane = token row tr of the block; columns = tile rows: [gate 32 | up 32 | gate 32 | up 32] of 64 intermediate
@@ -606,6 +658,7 @@ __global__ void __launch_bounds__(224, 1)
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ __nv_bfloat16* s_dst[BM];
+  __shared__ __nv_bfloat16* s_peer[8];
   __shared__ float s_wt[BM];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -642,8 +695,12 @@ __global__ void __launch_bounds__(224, 1)
   launder(sf_x);
   launder(block_expert);
   launder(num_valid);
-  launder(ep.sorted_ids);
-  launder(ep.sorted_w);
+  const int32_t* sorted_ids = ep.sorted_ids;
+  const float* sorted_w = ep.sorted_w;
+  launder(sorted_ids);
+  launder(sorted_w);
+  const RowPlacer placer = make_placer(ep, s_peer);
+  __syncthreads();
   int n_blocks = __ldcg(num_valid) / BM;
   if (n_blocks < 0 || n_blocks > max_blocks) {
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
@@ -766,6 +823,9 @@ __global__ void __launch_bounds__(224, 1)
     const int et = threadIdx.x - 64;
     float* stage_f = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + CC::kStages * C::kStageBytes);
     uint32_t ui = 0;
+    bool have_ahead = false;
+    int ahead_sid = 0;
+    float ahead_wt = 0.0f;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       const bool second = u >= units1;
       const int v = second ? u - units1 : u;
@@ -774,11 +834,24 @@ __global__ void __launch_bounds__(224, 1)
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
       if (second && et < BM) {
-        s_dst[et] = slot_row(ep, __ldcg(ep.sorted_ids + row0 + et));
-        s_wt[et] = __ldcg(ep.sorted_w + row0 + et);
+        if (!have_ahead) {
+          ahead_sid = __ldcg(sorted_ids + row0 + et);
+          ahead_wt = __ldcg(sorted_w + row0 + et);
+        }
+        s_dst[et] = placer.row(ahead_sid);
+        s_wt[et] = ahead_wt;
       }
       if (!epilogue_all(mbar_wait(smem_u32(&bar_tfull[acc]), aph, abort_v, status), 1u)) break;
       tc_fence_after();
+      {  // look ahead: the rows of this CTA's next unit, when that is a GEMM2 unit
+        const int un = u + static_cast<int>(gridDim.x);
+        have_ahead = un < total_units && un >= units1;
+        if (have_ahead && et < BM) {
+          const int64_t r1 = static_cast<int64_t>((un - units1) / kW2Tiles) * BM + et;
+          ahead_sid = __ldcg(sorted_ids + r1);
+          ahead_wt = __ldcg(sorted_w + r1);
+        }
+      }
       const uint32_t t_acc = tmem_base + acc * C::kAccCols + (static_cast<uint32_t>(q * 32) << 16);
       if (!second) {
         float* mine = stage_f + (q >> 1) * 68 + (q & 1) * 32 + lane;
