@@ -77,7 +77,7 @@ extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, con
   if ((r = b200moe_quant_dispatch(x_bf16, ws.sorted_ids, ws.num_valid, tokens, ws.bm, ws.rows, ws.xq_sorted, ws.sfx,
                                   ws.done, stream)))
     return r;
-  if (ws.bm == 16) {  // up to 128 tokens: both grouped GEMMs in one persistent launch (measured faster there only)
+  if (tokens <= 32) {  // small batches: both grouped GEMMs in one persistent launch (measured faster there only)
     if ((r = b200moe_gemm12(w->w13t, w->w2t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.sorted_ids,
                             ws.sorted_w, ws.rows, ws.bm, tokens, ws.hq, ws.sfh, ws.done, slots_bf16, status, stream)))
       return r;
