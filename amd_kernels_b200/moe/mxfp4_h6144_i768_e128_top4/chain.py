@@ -431,7 +431,7 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     return (slots, None) if return_partials else out
 
 
-WARM_UP_TOKENS = (1, 64, 257, 513, 1025)  # one-launch GEMMs, then one size per block height (16, 32, 64, 128)
+WARM_UP_TOKENS = (1, 64, 257, 897, 1537)  # one-launch GEMMs, then one size per block height (16, 32, 64, 128)
 
 
 def warm_up_mxfp4_moe(w, *, partials=False, workers=None):
