@@ -79,12 +79,12 @@ class MoeWeights:
                        routed_scaling_factor=2.0, routing_mode="sigmoid_bias", keep_row_major=False):
         """Checkpoint layout (row-major uint8 MXFP4 codes / e8m0 scales, gate rows then up rows) -> the kernels'
         layouts. ``routing_mode``: "sigmoid_bias" (the reference's rule) or "softmax" (top-4 of the softmax,
-        renormalised). ``shared`` (the MXFP8 shared expert) is accepted and must be None in this build."""
+        renormalised). ``shared``: the MXFP8 shared expert's ``SharedWeights`` (or None: routed experts only)."""
         reason = unsupported_reason(w13, w13_scale, w2, w2_scale, None, None, None, None, routed_only=True)
         if reason is not None:
             raise ValueError(reason)
-        if shared is not None:
-            raise ValueError("the MXFP8 shared expert is not built: pass shared=None")
+        if shared is not None and not hasattr(shared, "stream"):
+            raise ValueError("shared= takes SharedWeights.from_row_major(...)")
         if routing_mode not in ROUTING_MODES:
             raise ValueError(f"routing_mode must be one of {sorted(ROUTING_MODES)}")
         if not w13.is_cuda:
@@ -102,7 +102,7 @@ class MoeWeights:
                        "preshuffle_w2")
         bias = None if correction_bias is None else correction_bias.to(device=dev, dtype=torch.float32).contiguous()
         return cls(router_weight, bias, w13t, None, w2t, None, float(routed_scaling_factor), routing_mode,
-                   shared_weights=None, row_major=(w13, w13_scale, w2, w2_scale) if keep_row_major else None)
+                   shared_weights=shared, row_major=(w13, w13_scale, w2, w2_scale) if keep_row_major else None)
 
     @property
     def num_experts(self) -> int:
@@ -121,7 +121,7 @@ class MoeWeights:
 def unsupported_reason(w13, w13_scale, w2, w2_scale, shared_w13, shared_s13, shared_w2, shared_s2,
                        swiglu=(1.702, 7.0, 1.0), *, routed_only=False) -> str | None:
     """None when ``MoeWeights.from_row_major`` takes these checkpoint-layout tensors, else the reason
-    (reference __init__.py:19-35). ``routed_only`` skips the shared-expert tensors, which this build does not use."""
+    (reference __init__.py:19-35). ``routed_only`` skips the shared-expert tensors (a layer without one)."""
     ref = (1.702, 7.0, 1.0)
     if any(abs(a - b) > 1e-6 for a, b in zip(swiglu, ref)):
         return f"needs SwiGLU-OAI (alpha, limit, beta) {ref}, got {tuple(swiglu)}"
@@ -404,9 +404,11 @@ def mxfp4_moe_experts(x_quant, topk_weights, topk_ids, w):
 def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     """Normed BF16 [M, 6144] -> the routed experts' output (reference chain.py:127-197).
 
-    Reduced mode returns BF16 [M, 6144] = slots 0..3 summed in fp32; partials mode returns (slots BF16 [M, 4, H], None)
-    (the second item is the shared expert's output in the reference). ``router_logits`` fp32 [M, E] skips the router
-    GEMM. One call = one ``b200moe_forward`` on the current stream; scratch and outputs come from ``torch.empty``."""
+    Reduced mode returns BF16 [M, 6144] = slots 0..3, then the shared expert's output, summed in fp32; partials mode
+    returns (slots BF16 [M, 4, H], shared BF16 [M, H]); without ``w.shared_weights`` the shared term is absent (None).
+    ``router_logits`` fp32 [M, E] skips the router GEMM. The routed part is one ``b200moe_forward`` on the current
+    stream; the shared expert runs on the device's side stream beside it and the current stream joins it before the
+    reduce. Scratch and outputs come from ``torch.empty``."""
     if not isinstance(x, torch.Tensor):
         raise ValueError("prepared inputs (MoeInput / MoeInputCompact) are not built")
     variant_for(x.shape[0])
@@ -414,7 +416,15 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
         raise ValueError("expected contiguous BF16 [M,6144]")
     lib = _lib.load()
     n, dev = x.shape[0], x.device
+    sw = w.shared_weights
+    shared = None
+    if sw is not None:
+        from .shared_expert import shared_expert_parallel
+        current = torch.cuda.current_stream(dev)
+        shared = shared_expert_parallel(x, sw, current)
     logits = _logits(x, w, router_logits)
+    if sw is not None:
+        return _with_shared(x, w, logits, shared, return_partials)
     if logits.ndim == 3:
         # split-K partials from the router GEMM: the top-4 kernel adds them in split order, then the stages run one by one
         wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
@@ -429,6 +439,27 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
                                    _ptr(slots), _ptr(out), _ptr(status_word(dev)), _stream(dev)), "forward")
     return (slots, None) if return_partials else out
+
+
+def _with_shared(x, w, logits, shared, return_partials):
+    """The routed slots on the current stream, then the join with the side stream and the reduce with the shared term."""
+    lib = _lib.load()
+    n, dev = x.shape[0], x.device
+    if logits.ndim == 3:
+        wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
+        sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
+        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w)
+        slots = grouped_gemm2(hq, sfh, sort, w)
+    else:
+        ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        slots = torch.empty((n, TOPK, H), dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
+                                       _ptr(slots), None, _ptr(status_word(dev)), _stream(dev)), "forward")
+    current = torch.cuda.current_stream(dev)
+    current.wait_stream(w.shared_weights.stream)
+    shared.record_stream(current)
+    return (slots, shared) if return_partials else reduce_slots(slots, shared)
 
 
 WARM_UP_TOKENS = (1, 64, 257, 897, 1537)  # one-launch GEMMs, then one size per block height (16, 32, 64, 128)

@@ -202,6 +202,32 @@ int b200moe_gemm2_simt(const uint8_t* w2, const uint8_t* w2_scale, const uint8_t
  * out = bf16( (((+0 + s0) + s1) + s2) + s3 (+ shared) ) in fp32, bit-exact. shared may be null. */
 int b200moe_reduce_slots(const void* slots_bf16, const void* shared_bf16, int64_t tokens, void* out_bf16, void* stream);
 
+/* ---- the MXFP8 shared expert (MOE/shared_expert.py: SharedWeights, shared_expert; oracle MOE/reference.py:162-189
+ * shared_mxfp8_quant_ref / shared_mxfp8_ref): a dense SwiGLU-OAI MLP on every token, E4M3 codes with one E8M0 scale
+ * per 32 elements for weights, the input and the SwiGLU output; fp32 accumulation; bf16 result rows.
+ *
+ * b200moe_preshuffle_shared: row-major w13 E4M3 [1536][6144] + scales [1536][192], w2 E4M3 [6144][768] + scales
+ * [6144][24] (the layout MOE/__init__.py:19-31 unsupported_reason checks) -> tile records: w13t 12*48 and w2t 48*6
+ * records of 17408 bytes (16384 swizzled code bytes, one 512-byte scale atom, padding). W13 tiles interleave gate and
+ * up rows like the routed ones. */
+int b200moe_preshuffle_shared(const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2, const uint8_t* w2_scale,
+                              uint8_t* w13t, uint8_t* w2t, void* stream);
+#define B200MOE_SHARED_W13T_BYTES (12 * 48 * 17408)
+#define B200MOE_SHARED_W2T_BYTES (48 * 6 * 17408)
+
+/* Input quantiser of the shared expert (MOE/reference.py:162-171 shared_mxfp8_quant_ref: scale = ceil_pow2(amax/448),
+ * exponent byte >= 1, round to nearest even), bit-exact. x bf16 [T][6144] -> codes8 [ceil(T/bm)*bm][6144] (padding
+ * rows zero) and scale atoms [ceil(T/bm)][48][512]: row r of a block keeps scale j of K-tile a at byte
+ * a*512 + (r%32)*16 + (r/32)*4 + j. bm in {16,32,64,128}. */
+int b200moe_shared_quant(const void* x_bf16, int64_t tokens, int bm, uint8_t* codes8, uint8_t* atoms, void* stream);
+
+/* The shared expert on one stream (MOE/shared_expert.py shared_expert): quantise -> GEMM1 + SwiGLU-OAI + MXFP8
+ * requantise -> GEMM2 -> out bf16 [T][6144]. workspace: b200moe_shared_workspace_bytes(T) bytes, 256-byte aligned.
+ * status as in the routed kernels. */
+size_t b200moe_shared_workspace_bytes(int64_t tokens);
+int b200moe_shared_expert(const uint8_t* w13t, const uint8_t* w2t, const void* x_bf16, int64_t tokens, void* workspace,
+                          size_t workspace_bytes, void* out_bf16, int32_t* status, void* stream);
+
 /* The same reduce over slot rows that sit in another order: index int32 [T][4] gives, for pair 4*token+slot, its row in
  * rows_bf16 [N][6144] (the expert-parallel combine: rows come back from the other ranks in send order). Same arithmetic
  * and the same bits as b200moe_reduce_slots on the reordered rows. No counterpart in the reference (it has no expert

@@ -207,6 +207,80 @@ def moe_layer(x_bits, logits, w13, w13_scale, w2, w2_scale, *, mode="softmax", b
     return dict(out=reduce_slots_bf16(slot_bits), slots=slot_bits, ids=ids.astype(np.int32), weights=w32, xq=xq, xs=xs)
 
 
+# ----------------------------------------------------------------------------------------------- shared expert (MXFP8)
+def _e4m3_table() -> np.ndarray:
+    """float32 value of every E4M3 (fn) byte; 0x7f / 0xff are NaN."""
+    codes = np.arange(256, dtype=np.uint32)
+    sign = np.where(codes & 0x80, -1.0, 1.0)
+    exp = (codes >> 3) & 0xF
+    man = codes & 7
+    val = np.where(exp == 0, man / 8.0 * 2.0 ** -6, (1.0 + man / 8.0) * np.exp2(exp.astype(np.float64) - 7.0))
+    val = np.where((codes & 0x7F) == 0x7F, np.nan, val)
+    return (sign * val).astype(np.float32)
+
+
+E4M3 = _e4m3_table()
+
+
+def e4m3_to_f32(codes: np.ndarray) -> np.ndarray:
+    return E4M3[codes]
+
+
+def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
+    """float32 -> E4M3 bytes, round to nearest, ties to the even code, |x| <= 448 (what ``.to(torch.float8_e4m3fn)``
+    does for in-range values; the quantiser below never leaves the range)."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x).astype(np.float64)
+    pos = E4M3[:127].astype(np.float64)  # codes 0..126 ascend with their values
+    hi = np.clip(np.searchsorted(pos, a, side="left"), 1, 126)
+    lo = hi - 1
+    d_lo, d_hi = a - pos[lo], pos[hi] - a
+    code = np.where(d_lo < d_hi, lo, np.where(d_hi < d_lo, hi, np.where(lo % 2 == 0, lo, hi)))
+    code = np.where(a >= 448.0, 126, code)
+    return (code.astype(np.uint8) | (np.signbit(x).astype(np.uint8) << 7)).astype(np.uint8)
+
+
+def shared_mxfp8_quant(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """float32 [.., K] -> (E4M3 codes u8 [.., K], E8M0 u8 [.., K/32]); scale = ceil_pow2(amax / 448), exponent >= 1, no
+    bf16 rounding first (reference.py:162-171)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    v = x.reshape(*x.shape[:-1], x.shape[-1] // 32, 32)
+    u = (np.abs(v).max(-1) / np.float32(448.0)).astype(np.float32).view(np.int32)
+    e = (u >> 23) & 255
+    e = np.maximum(e + (((u & 0x7FFFFF) != 0) & (e < 255)), 1)
+    q = f32_to_e4m3((v / np.exp2(e.astype(np.float32) - 127.0)[..., None]).astype(np.float32))
+    return q.reshape(x.shape), e.astype(np.uint8)
+
+
+def dequant_shared_mxfp8(q: np.ndarray, s: np.ndarray) -> np.ndarray:
+    """(reference.py:174-175)"""
+    return e4m3_to_f32(q) * np.repeat(np.exp2(s.astype(np.float32) - 127.0), 32, axis=-1)
+
+
+def shared_mxfp8(x: np.ndarray, w13, s13, w2, s2) -> np.ndarray:
+    """The shared expert in float32 (reference.py:178-189, quantized=True): x and the SwiGLU output go through the
+    MXFP8 quantiser, both GEMMs and SwiGLU-OAI run in float32."""
+    xq = dequant_shared_mxfp8(*shared_mxfp8_quant(x))
+    gu = xq @ dequant_shared_mxfp8(w13, s13).T
+    inter = w13.shape[0] // 2
+    h = dequant_shared_mxfp8(*shared_mxfp8_quant(swiglu_oai(gu[:, :inter], gu[:, inter:])))
+    return (h @ dequant_shared_mxfp8(w2, s2).T).astype(np.float32)
+
+
+def make_shared_weights(seed: int = 607, hidden: int = H, inter: int = I):
+    """Random MXFP8 shared-expert weights, the recipe of the reference's tests/moe/.../workload.py:48-61 with a CPU
+    generator: E4M3 codes of 20*N(0,1), E8M0 bytes uniform in [118, 124)."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+
+    def weight(n, k):
+        q = f32_to_e4m3((torch.randn((n, k), generator=g) * 20).numpy())
+        s = torch.randint(118, 124, (n, k // 32), dtype=torch.uint8, generator=g).numpy()
+        return q, s
+
+    return (*weight(2 * inter, hidden), *weight(hidden, inter))
+
+
 # ----------------------------------------------------------------------------------------------- input recipes
 def make_weights(seed: int = 0, experts: int = E, hidden: int = H, inter: int = I, scale_lo: int = 120,
                  scale_hi: int = 125):

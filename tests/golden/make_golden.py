@@ -12,6 +12,7 @@ Fixtures (inputs are stored or re-derivable from the stated seed; outputs come f
   swiglu.npz   fp32 gate / up                                  -> swiglu_oai
   reduce.npz   bf16 slots incl. signed zeros and subnormals    -> reduce_slots_bf16_ref
   moe_small.npz  E=8, H=256, I=64, T=32 MXFP4 layer            -> w4a4_moe_ref
+  shared.npz   bf16 rows -> shared_mxfp8_quant_ref; seeded MXFP8 weights -> shared_mxfp8_ref; torch's E4M3 cast
   moe_config0.npz  the benchmark's configuration 0 (T=16, E=128, H=6144, I=768, seed 0; inputs re-derived from the seed
                by oracle.moe_oracle.make_weights / make_inputs, their CRC32 stored) -> w4a4_moe_ref on softmax top-4
                routing, and on the reference's sigmoid+bias routing
@@ -116,6 +117,23 @@ def main():
                         weights_softmax=wts.astype(np.float32), ids_softmax=tid.astype(np.int32), out_softmax=out_soft.numpy(),
                         weights_sigmoid=wsig.numpy(), ids_sigmoid=isig.numpy().astype(np.int32), vals_sigmoid=vsig.numpy(),
                         out_sigmoid=out_sig.numpy())
+    # ---- shared expert (MXFP8)
+    g = torch.Generator().manual_seed(21)
+    xs = (torch.randn((16, 6144), generator=g) * torch.exp2(torch.randint(-6, 7, (16, 192), generator=g).float()
+                                                            ).repeat_interleave(32, 1)).bfloat16()
+    xs[0, :64] = 0
+    xs[1, :32] = torch.tensor([448.0, 224.0, 0.875, -0.0, 1.0625, 1.1875, 30.0, 31.0] * 4)  # E4M3 ties and the top value
+    q8, s8 = ref.shared_mxfp8_quant_ref(xs)
+    sw13, ss13, sw2, ss2 = orc.make_shared_weights()
+    tsw = [torch.from_numpy(sw13).view(torch.float8_e4m3fn), torch.from_numpy(ss13), torch.from_numpy(sw2).view(torch.float8_e4m3fn),
+           torch.from_numpy(ss2)]
+    torch_codes = (torch.randn((64, 256), generator=torch.Generator().manual_seed(3)) * 20).to(torch.float8_e4m3fn)
+    out_shared = ref.shared_mxfp8_ref(xs, *tsw)
+    np.savez_compressed(os.path.join(HERE, "shared.npz"), x_bits=bits(xs), codes=q8.numpy(), scales=s8.numpy(),
+                        out=out_shared.numpy(), weight_crc=np.array([zlib.crc32(a.tobytes()) for a in (sw13, ss13, sw2, ss2)],
+                                                                    dtype=np.uint32),
+                        cast_in=(torch.randn((64, 256), generator=torch.Generator().manual_seed(3)) * 20).numpy(),
+                        cast_codes=torch_codes.view(torch.uint8).numpy())
     print("golden fixtures written to", HERE)
 
 

@@ -109,3 +109,15 @@ def test_moe_config0_matches_reference(config0):
     dec = orc.decided(vals)
     assert np.array_equal(isig[dec], g["ids_sigmoid"][dec])
     np.testing.assert_allclose(wsig, g["weights_sigmoid"], rtol=1e-12)
+
+
+def test_shared_expert_quant_cast_and_mlp_match_reference():
+    g = golden("shared.npz")
+    assert np.array_equal(orc.f32_to_e4m3(g["cast_in"]), g["cast_codes"])           # torch's E4M3 cast, ties included
+    q, s = orc.shared_mxfp8_quant(orc.bf16_to_f32(g["x_bits"]))
+    assert np.array_equal(s, g["scales"]) and np.array_equal(q, g["codes"])
+    weights = orc.make_shared_weights()
+    assert [zlib.crc32(a.tobytes()) for a in weights] == g["weight_crc"].tolist()
+    out = orc.shared_mxfp8(orc.bf16_to_f32(g["x_bits"]), *weights)
+    rel = np.linalg.norm(out - g["out"]) / np.linalg.norm(g["out"])
+    assert rel < 2e-3, rel  # FP8 codes of h that flip on fp32 summation order
