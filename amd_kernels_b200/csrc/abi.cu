@@ -85,7 +85,7 @@ extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, con
     return 0;
   }
   if ((r = b200moe_gemm1_swiglu_quant(w->w13t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows, ws.bm,
-                                      ws.hq, ws.sfh, status, stream)))
+                                      ws.hq, ws.sfh, w->w2t, status, stream)))
     return r;
   if ((r = b200moe_gemm2_weighted(w->w2t, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids, ws.sorted_w,
                                   ws.rows, ws.bm, tokens, slots_bf16, status, stream)))

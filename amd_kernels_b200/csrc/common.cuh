@@ -48,6 +48,11 @@ __device__ __forceinline__ void pdl_enter(P&... ptrs) {
   (launder(ptrs), ...);
 }
 
+// ask L2 to fetch `bytes` (a multiple of 16) at a 16-byte aligned global address; no register or shared-memory destination
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(p)), "r"(bytes) : "memory");
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                      Args... args) {

@@ -63,6 +63,7 @@ struct EpilogueArgs {
   // GEMM1
   uint8_t* hq;
   uint8_t* sfh;
+  const uint8_t* next_tiles;  // GEMM1, may be null: the W2 tile records, prefetched into L2 for the GEMM2 that follows
   // GEMM2
   const int32_t* sorted_ids;
   const float* sorted_w;
@@ -215,6 +216,17 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
           bulk_load(base, w_src + static_cast<int64_t>(kt) * kTileRecordBytes, kTileRecordBytes, full);
           tma_load_2d(base + C::kBOffset, &map_x, kt * 128, b * BM, full);
           bulk_load(base + C::kSfbOffset, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
+        }
+      }
+      if (MODE == 1 && ok && ep.next_tiles != nullptr) {
+        // This CTA's weight stream has ended: ask L2 for the W2 tiles that the following GEMM2 reads first (its unit u2 =
+        // row block u2 / 48, tile u2 % 48; four rounds of one unit per SM), while the slower CTAs finish.
+        const int lim = total_units / C::kTilesM * kW2Tiles < 592 ? total_units / C::kTilesM * kW2Tiles : 592;
+        for (int u2 = blockIdx.x; u2 < lim; u2 += gridDim.x) {
+          const int e = __ldcg(block_expert + u2 / kW2Tiles);
+          if (e >= 0 && e < num_experts)
+            l2_prefetch_bulk(ep.next_tiles + static_cast<int64_t>(e * kW2Tiles + u2 % kW2Tiles) * kK2Tiles * kTileRecordBytes,
+                             kK2Tiles * kTileRecordBytes);
         }
       }
       if (!ok) {
@@ -929,8 +941,8 @@ extern "C" int b200moe_gemm12(const uint8_t* w13t, const uint8_t* w2t, int num_e
 
 extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted,
                                           const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
-                                          int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh, int32_t* status,
-                                          void* stream) {
+                                          int64_t max_rows, int bm, uint8_t* hq, uint8_t* sfh,
+                                          const uint8_t* prefetch_w2t, int32_t* status, void* stream) {
   using namespace b200moe;
   if (!w13t || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status) return B200MOE_E_ARG;
   if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || (bm != 16 && bm != 32 && bm != 64 && bm != 128) ||
@@ -946,6 +958,7 @@ extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, 
   EpilogueArgs ep{};
   ep.hq = hq;
   ep.sfh = sfh;
+  ep.next_tiles = misaligned(prefetch_w2t, 16) ? nullptr : prefetch_w2t;
   return launch_bm<1>(bm, mx, w13t, sfx, block_expert, num_valid, ep, max_rows, num_experts, status,
                       static_cast<cudaStream_t>(stream));
 }

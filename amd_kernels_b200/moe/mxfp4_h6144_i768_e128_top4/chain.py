@@ -251,14 +251,16 @@ def route_sort(logits: torch.Tensor, w: "MoeWeights", bm: int | None = None):
     return wt, ids, buf
 
 
-def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
-    """GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 -> (h codes [rows, 384], h scale atoms [rows/bm, 6, 512])."""
+def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_next: bool = False):
+    """GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 -> (h codes [rows, 384], h scale atoms [rows/bm, 6, 512]).
+    ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first."""
     dev = xq_sorted.device
     hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
     _lib.check(_lib.load().b200moe_gemm1_swiglu_quant(_ptr(w.w13), w.num_experts, _ptr(xq_sorted),
                                                       _ptr(sfx), _ptr(sort.block_expert), _ptr(sort.num_valid),
                                                       sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
+                                                      _ptr(w.w2) if prefetch_next else None,
                                                       _ptr(status_word(dev)), _stream(dev)), "gemm1_swiglu_quant")
     return hq, sfh
 
@@ -429,7 +431,7 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
         # split-K partials from the router GEMM: the top-4 kernel adds them in split order, then the stages run one by one
         wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
         sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
-        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w)
+        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w, prefetch_next=True)
         slots = grouped_gemm2(hq, sfh, sort, w)
         return (slots, None) if return_partials else reduce_slots(slots)
     ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
@@ -448,7 +450,7 @@ def _with_shared(x, w, logits, shared, return_partials):
     if logits.ndim == 3:
         wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
         sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
-        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w)
+        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w, prefetch_next=True)
         slots = grouped_gemm2(hq, sfh, sort, w)
     else:
         ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))

@@ -3,7 +3,7 @@
 Workload: global T tokens (default 16384) split evenly over the W ranks; 128/W experts per rank; every step is one
 layer call on every rank (route, quantise, all-to-all dispatch, grouped GEMMs, all-to-all combine, fixed-order reduce).
 Total work is fixed as W grows ("strong" scaling). Per-step device time is taken with CUDA events on each rank after an
-untimed L2 flush; the job's time is the maximum over the ranks of the summed step times."""
+untimed L2 flush (written, then evicted by a read); the job's time is the maximum over the ranks of the summed step times."""
 from __future__ import annotations
 
 import json
@@ -53,7 +53,10 @@ def run(args):
     if zipf:
         skew = -2.2 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
         lgs = [lg + skew for lg in lgs]
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))))
+    from bench import ClockSampler, L2Flush, workload_config, FLOPS_PER_TOKEN, measured_peaks
+    flush = L2Flush(torch)
     hx = [t.cpu().pin_memory() for t in xs]
     hl = [t.cpu().pin_memory() for t in lgs]
     hout = torch.empty((t_loc, H), dtype=torch.bfloat16).pin_memory()
@@ -93,9 +96,6 @@ def run(args):
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         return mx[0].item(), mx[1].item(), mx[2].item(), sm[3].item() / world
 
-    import sys
-    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))))
-    from bench import ClockSampler, workload_config, FLOPS_PER_TOKEN, measured_peaks
     clocks = ClockSampler(local)
     with clocks:
         total_ms, wall_ms, max_rows, mean_rows = timed(step, args.steps, args.warmup)
@@ -116,7 +116,7 @@ def run(args):
                     "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
                     else "NCCL all-to-all of bf16 slot rows",
                     "max_rows_received_by_a_rank": max_rows, "mean_rows_received_per_rank": mean_rows,
-                    "timing": "CUDA events per step on every rank after an untimed 512 MB L2 flush, max over ranks"})
+                    "timing": "CUDA events per step on every rank after the untimed L2 flush, max over ranks"})
         line = {"metric": "moe_layer_tokens_per_s", "value": tokens_global / (per_step * 1e-3), "unit": "tokens/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4", "data": "synthetic",

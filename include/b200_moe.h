@@ -147,10 +147,11 @@ int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const int32_t* se
 /* Grouped GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 block-scaled FP4 MMA
  * (MOE/gemm1_prefill_h6144_i768.py:71-898, MOE/gemm1_a4w4_small.py:75-164; oracle MOE/reference.py:66-72).
  * hq [max_rows][384] codes of h in sorted-row order, sfh [max_rows/bm][6][512] scale atoms. All pointers 16-byte
- * aligned. `status` (device int32) receives B200MOE_DEV_* codes. */
+ * aligned. `status` (device int32) receives B200MOE_DEV_* codes. `prefetch_w2t` (may be null): the W2 tile records;
+ * each CTA, once its own weight stream has ended, then asks L2 for the tiles a following GEMM2 reads first. */
 int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
                                const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, int bm,
-                               uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream);
+                               uint8_t* hq, uint8_t* sfh, const uint8_t* prefetch_w2t, int32_t* status, void* stream);
 
 /* Grouped GEMM2, times the routing weight, rounded to bf16, one writer per (token, slot, column)
  * (MOE/gemm2_a4w4_small.py:19-79, MOE/gemm2_a4w4_bm128.py:52; oracle MOE/reference.py:73-74).
