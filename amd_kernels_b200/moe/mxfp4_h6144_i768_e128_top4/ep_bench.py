@@ -32,6 +32,35 @@ def build_rank_layer(rank, world, placement, seed=0, peer_pairs=0):
                                 peer_pairs=peer_pairs)
 
 
+def one_gpu_same_workload(chain, flush, tokens, zipf, steps):
+    """Rank 0 alone: the same global token count through the single-GPU layer (all 128 experts on this GPU), timed the
+    same way, so the strong-scaling ratio can be read from one JSON line. The other ranks wait at the final barrier."""
+    from oracle import moe_oracle as orc
+    raw, _ = orc.make_weights(seed=0)
+    w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(a).cuda() for a in raw), routing_mode="softmax",
+                                        routed_scaling_factor=1.0)
+    del raw
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    x = torch.randn((tokens, H), device="cuda", generator=gen).bfloat16()
+    lg = torch.randn((tokens, E), device="cuda", generator=gen)
+    if zipf:
+        lg = lg - 2.2 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
+    with torch.inference_mode():
+        for i in range(3):
+            flush.fill_(i)
+            chain.mxfp4_moe(x, w, router_logits=lg)
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i in range(steps):
+            flush.fill_(i)
+            ev[i][0].record()
+            chain.mxfp4_moe(x, w, router_logits=lg)
+            ev[i][1].record()
+        torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / steps
+    return {"ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": "tokens/s"}
+
+
 def run(args):
     from . import chain
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -111,6 +140,7 @@ def run(args):
         link_bytes = mean_rows * remote * (ROW_BYTES_IN + ROW_BYTES_OUT)
         t_link = link_bytes / (NVLINK_GBS_MEASURED * 1e9)
         t_fp4 = tokens_global / world * FLOPS_PER_TOKEN / (4 * peaks["bf16_tflops"] * 1e12)
+        one_gpu = one_gpu_same_workload(chain, flush, tokens_global, zipf, args.steps)
         cfg = workload_config(tokens_global, world)
         cfg.update({"tokens_per_rank": t_loc, "expert_placement": placement, "routing_skew": "zipf 1.1" if zipf else "none",
                     "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
@@ -128,6 +158,7 @@ def run(args):
                              "nvlink_bytes_per_rank_per_direction": link_bytes, "nvlink_gbs_peak": NVLINK_GBS_MEASURED,
                              "traffic": None},
                 "cpu_baseline": None,
+                "one_gpu_same_workload": one_gpu,
                 "e2e": {"value": tokens_global / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                         "h2d_bytes_per_step": tokens_global * (2 * H + 4 * E), "d2h_bytes_per_step": tokens_global * 2 * H},
                 "gpu_launches": args.steps * 8, "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks.summary()}

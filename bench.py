@@ -191,8 +191,9 @@ class Layer:
         return sum(n) / len(n)
 
     def launches_per_step(self):
-        # route+sort fused up to 32 tokens, split above (plus a count pass above 256), quantise+gather, two GEMMs, reduce
-        return 5 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
+        # up to 32 tokens: route+sort, quantise+gather, both GEMMs in one launch, reduce; above: routing and sort apart
+        # (plus a count pass above 256), quantise+gather, two GEMMs, reduce
+        return 4 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
 
 
 class L2Flush:
@@ -230,6 +231,35 @@ def time_steps(torch, fn, steps, warmup, flush):
         stops[i].record()
     torch.cuda.synchronize()
     return [a.elapsed_time(b) for a, b in zip(starts, stops)]
+
+
+def with_shared_expert(torch, chain, orc, w, layer, flush, args):
+    """The same workload through the package entry with the MXFP8 shared expert (its three launches on the device's side
+    stream, joined before the reduce), as CUDA-graph replays; reported beside the headline, not in it."""
+    from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import shared_expert as S
+    sw = S.SharedWeights.from_row_major(*(torch.from_numpy(a).cuda() for a in orc.make_shared_weights()))
+    w1 = chain.MoeWeights(None, None, w.w13, None, w.w2, None, w.routed_scaling_factor, w.routing_mode, shared_weights=sw)
+    with torch.inference_mode():
+        chain.mxfp4_moe(layer.x[0], w1, router_logits=layer.logits[0])
+        S.shared_expert(layer.x[0], sw)
+        torch.cuda.synchronize()
+        graphs, alone, keep = [], [], []
+        for i in range(len(layer.x)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep.append(chain.mxfp4_moe(layer.x[i], w1, router_logits=layer.logits[i]))
+            graphs.append(g)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep.append(S.shared_expert(layer.x[i], sw))
+            alone.append(g)
+        ms = time_steps(torch, lambda i: graphs[i % len(graphs)].replay(), args.steps, args.warmup, flush)
+        ms_alone = time_steps(torch, lambda i: alone[i % len(alone)].replay(), args.steps, args.warmup, flush)
+    t = sum(ms) / len(ms)
+    return {"us_per_step": t * 1e3, "tokens_per_s": layer.tokens / (t * 1e-3),
+            "shared_expert_alone_us": sum(ms_alone) / len(ms_alone) * 1e3,
+            "launches_per_step": layer.launches_per_step() + 3,
+            "note": "routed layer + MXFP8 shared expert (quantise, GEMM1+SwiGLU+requantise, GEMM2) summed in the reduce"}
 
 
 def roofline_times(tokens, e_active, peaks):
@@ -313,6 +343,7 @@ def single_gpu(args):
             torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
         e2e_wall = time.perf_counter() - t0
         e2e_ms = time_steps(torch, e2e_step, args.steps, 1, flush)
+        shared_rep = with_shared_expert(torch, chain, orc, w, layer, flush, args)
     status = chain.last_status()
     if status:
         raise RuntimeError(f"device status {status}: a kernel wait timed out")
@@ -339,6 +370,7 @@ def single_gpu(args):
             "e2e": {"value": headline_t / (sum(e2e_ms) / len(e2e_ms) * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": headline_t * (2 * H + 4 * E), "d2h_bytes_per_step": headline_t * 2 * H,
                     "wall_value_with_sync_per_step": headline_t * args.steps / e2e_wall},
+            "with_shared_expert": shared_rep,
             "gpu_launches": args.steps * layer.launches_per_step(),
             "clocks": clocks.summary(), "sweep": sweep}
     print(json.dumps(line))
