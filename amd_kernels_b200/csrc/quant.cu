@@ -132,8 +132,8 @@ struct PushArgs {
   uint8_t* codes[8];
   uint8_t* scales[8];
   int32_t* meta[8];
-  int64_t dst_base[8];   // first row of this rank's segment in each destination's buffers
-  int32_t seg_start[8];  // first send row that goes to each destination
+  const int64_t* dst_base;   // device [world]: first row of this rank's segment in each destination's buffers
+  const int32_t* seg_start;  // device [world]: first send row that goes to each destination
   int32_t world, rank, experts_per_rank, interleaved;
   int64_t capacity;      // rows every receive buffer holds
 };
@@ -144,20 +144,22 @@ __global__ void __launch_bounds__(256) quant_push_kernel(const uint4* __restrict
                                                          const int32_t* __restrict__ send_rank, int64_t tokens,
                                                          PushArgs a, int32_t* status) {
   constexpr int kIters = kH / 8 / 256;  // 3
+  __shared__ __align__(16) uint32_t s_codes[kH / 8];   // the row's 3072 code bytes
+  __shared__ __align__(16) uint32_t s_scales[kH / 128];  // and its 192 scale bytes
   const int lane = threadIdx.x & 31;
   const int64_t i = blockIdx.x;
   const int sid = send_ids[i];
   const int64_t token = sid & 0x00ffffff;
   const int slot = (sid >> 24) & 3, d = send_rank[i];
   if (token >= tokens || d < 0 || d >= a.world) return;
-  const int64_t row = a.dst_base[d] + (i - a.seg_start[d]);
+  const int64_t row = __ldg(a.dst_base + d) + (i - __ldg(a.seg_start + d));
   if (row < 0 || row >= a.capacity) {  // never store outside a receive buffer
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
     return;
   }
   const uint4* src = x + token * (kH / 8);
-  uint32_t* dst = reinterpret_cast<uint32_t*>(a.codes[d] + row * (kH / 2));
-  uint32_t* sdst = reinterpret_cast<uint32_t*>(a.scales[d] + row * (kH / 32));
+  uint4* dst = reinterpret_cast<uint4*>(a.codes[d] + row * (kH / 2));
+  uint4* sdst = reinterpret_cast<uint4*>(a.scales[d] + row * (kH / 32));
   uint4 raw[kIters];
 #pragma unroll
   for (int it = 0; it < kIters; ++it) raw[it] = src[it * 256 + threadIdx.x];
@@ -181,12 +183,17 @@ __global__ void __launch_bounds__(256) quant_push_kernel(const uint4* __restrict
     uint32_t packed = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
-    dst[idx] = packed;
+    s_codes[idx] = packed;
     uint32_t sc = static_cast<uint32_t>(e);
     sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
     sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
-    if ((lane & 15) == 0) sdst[idx >> 4] = sc;  // scale bytes 4*(idx/16) .. +3 of the row
+    if ((lane & 15) == 0) s_scales[idx >> 4] = sc;  // scale bytes 4*(idx/16) .. +3 of the row
   }
+  // the row leaves as 16-byte stores (a warp writes 512 contiguous bytes): full-size packets when the destination is a
+  // peer's buffer over NVLink
+  __syncthreads();
+  if (threadIdx.x < kH / 32) dst[threadIdx.x] = reinterpret_cast<const uint4*>(s_codes)[threadIdx.x];
+  else if (threadIdx.x < kH / 32 + kH / 512) sdst[threadIdx.x - kH / 32] = reinterpret_cast<const uint4*>(s_scales)[threadIdx.x - kH / 32];
   if (threadIdx.x == 0) {
     const int e = ids[token * kTopK + slot];
     const int local = a.interleaved ? e / a.world : e % a.experts_per_rank;
@@ -215,13 +222,13 @@ extern "C" int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const 
     a.codes[r] = static_cast<uint8_t*>(peer_codes[k]);
     a.scales[r] = static_cast<uint8_t*>(peer_scales[k]);
     a.meta[r] = static_cast<int32_t*>(peer_meta[k]);
-    a.dst_base[r] = dst_base[k];
-    a.seg_start[r] = seg_start[k];
     if (!a.codes[r] || !a.scales[r] || !a.meta[r]) return B200MOE_E_ARG;
     if ((reinterpret_cast<uintptr_t>(a.codes[r]) | reinterpret_cast<uintptr_t>(a.scales[r]) |
          reinterpret_cast<uintptr_t>(a.meta[r])) & 15)
       return B200MOE_E_ALIGN;
   }
+  a.dst_base = dst_base;
+  a.seg_start = seg_start;
   a.world = world;
   a.rank = rank;
   a.experts_per_rank = experts_per_rank;

@@ -142,7 +142,15 @@ class ExpertParallelMoe:
         if experts % self.world or weights.num_experts != experts // self.world:
             raise ValueError(f"needs {experts // self.world} local experts on each of {self.world} ranks")
         self.bias, self.mode, self.scale, self.placement, self.experts = bias, routing_mode, float(scale), placement, experts
-        self.last_recv_rows = 0
+        self.last_recv_rows, self._recv_rows = 0, None
+        if self.peer is not None:
+            self._ranks = torch.arange(self.world, device="cuda")
+            self._rows = torch.arange(self.peer.capacity, device="cuda")
+
+    @property
+    def recv_rows(self) -> int:
+        """Rows this rank received in the last call (reads the device count of the fused form: synchronises)."""
+        return int(self._recv_rows.item()) if self._recv_rows is not None else self.last_recv_rows
 
     def experts_on_rows(self, codes, scales, local_expert, weight, n, row_rank=None, row_pair=None):
         """The grouped GEMMs on rows that arrived from any rank: row r < n -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r.
@@ -180,7 +188,7 @@ class ExpertParallelMoe:
         send_counts, recv_counts = torch.stack([counts, arrived]).tolist()
         n = sum(recv_counts)
         padded = (n + TOPK - 1) // TOPK * TOPK
-        self.last_recv_rows = n
+        self.last_recv_rows, self._recv_rows = n, None
         src_token = order // TOPK
         meta = torch.stack([local[order].int(), wt.reshape(-1)[order].view(torch.int32)], dim=1)
 
@@ -211,41 +219,38 @@ class ExpertParallelMoe:
         """The fused form: (1) the pairs are grouped by destination rank by the routing-sort kernel; (2) one kernel
         quantises every pair's row and stores it into the destination's receive buffers; (3) the grouped GEMMs run on
         what arrived and GEMM2 stores every result row into its owner's slot buffer; (4) the owner reduces. Between the
-        phases one tiny all-reduce orders the ranks; the only host read is the W x W matrix of row counts."""
+        phases one tiny all-reduce orders the ranks. Nothing is read by the host: the W x W matrix of row counts stays on
+        the device, so the step can run ahead of the CPU and be captured in a CUDA graph."""
         import ctypes
         from . import chain
         from ... import _lib
         tokens, dev, peer = x.shape[0], x.device, self.peer
         dest, _ = expert_owner(ids, self.world, self.experts, self.placement)
         send = chain.moe_sort(dest.int().contiguous(), wt, 1, self.world)     # send order: pairs grouped by rank
-        counts = torch.bincount(dest.reshape(-1), minlength=self.world)
+        counts = (dest.reshape(-1, 1) == self._ranks).sum(0)                  # rows to every rank (no host read)
         matrix = torch.empty((self.world, self.world), dtype=counts.dtype, device=dev)
-        dist.all_gather_into_tensor(matrix, counts, group=self.group)
-        m = matrix.tolist()                                                   # m[s][d] rows from rank s to rank d
-        seg_start, run = [], 0
-        for d in range(self.world):
-            seg_start.append(run)
-            run += m[self.rank][d]
-        dst_base = [sum(m[s][d] for s in range(self.rank)) for d in range(self.world)]
-        n = sum(m[s][self.rank] for s in range(self.world))
-        padded = (n + TOPK - 1) // TOPK * TOPK
-        self.last_recv_rows = n
-        base_arr = (ctypes.c_int64 * self.world)(*dst_base)
-        seg_arr = (ctypes.c_int32 * self.world)(*seg_start)
+        dist.all_gather_into_tensor(matrix, counts, group=self.group)         # matrix[s][d]: rows from rank s to rank d
+        mine = matrix[self.rank]
+        seg_start = (torch.cumsum(mine, 0) - mine).int()                      # first send row for every destination
+        dst_base = matrix[:self.rank].sum(0)                                  # where this rank's segment starts there
+        n = matrix[:, self.rank].sum()                                        # rows this rank receives (device scalar)
+        self._recv_rows = n
         _lib.check(_lib.load().b200moe_quant_push(
             ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(send.sorted_ids.data_ptr()),
             ctypes.c_void_p(send.sorted_weights.data_ptr()), ctypes.c_void_p(send.block_expert.data_ptr()), tokens,
             self.world, self.rank, self.experts // self.world, int(self.placement == "interleaved"), peer.ptrs["codes"],
-            peer.ptrs["scales"], peer.ptrs["meta"], base_arr, seg_arr, peer.capacity,
+            peer.ptrs["scales"], peer.ptrs["meta"], ctypes.c_void_p(dst_base.data_ptr()),
+            ctypes.c_void_p(seg_start.data_ptr()), peer.capacity,
             ctypes.c_void_p(chain.status_word(dev).data_ptr()),
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "quant_push")
         dist.all_reduce(self._fence, group=self.group)                        # every rank's rows have landed
+        # the receive buffers are used at their full capacity: rows from n on (left over from earlier steps) get expert
+        # id -1 and are dropped by the sort, so the number of rows that arrived never has to reach the host
         meta = peer.local["meta"]
-        if padded > n:
-            meta[n:padded, 0] = -1                                            # rows beyond n are dropped by the sort
-        cols = meta[:padded].t().contiguous()                                 # expert, weight bits, source pair, source rank
-        self.experts_on_rows(peer.local["codes"][:padded], peer.local["scales"][:padded], cols[0],
-                             cols[1].view(torch.float32), n, cols[3], cols[2])
+        cols = meta.t().contiguous()                                          # expert, weight bits, source pair, source rank
+        cols[0].masked_fill_(self._rows >= n, -1)
+        self.experts_on_rows(peer.local["codes"], peer.local["scales"], cols[0], cols[1].view(torch.float32),
+                             peer.capacity, cols[3], cols[2])
         dist.all_reduce(self._fence, group=self.group)                        # every rank's result rows have landed
         slots = peer.local["slots"][:tokens * TOPK].view(tokens, TOPK, H)
         return slots.clone() if return_partials else chain.reduce_slots(slots)

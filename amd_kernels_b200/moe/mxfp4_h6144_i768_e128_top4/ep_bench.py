@@ -113,11 +113,12 @@ def run(args):
             ev[i][0].record()
             fn(warmup + i)
             ev[i][1].record()
-            recv.append(layer.last_recv_rows)
+            recv.append(layer._recv_rows if layer._recv_rows is not None else layer.last_recv_rows)
         torch.cuda.synchronize()
         dist.barrier()
         wall = time.perf_counter() - t0
         ms = sum(a.elapsed_time(b) for a, b in ev)
+        recv = [int(r) for r in recv]  # device counts of the fused form are read only now, after the timed region
         both = torch.tensor([ms, wall * 1e3, float(max(recv)), float(sum(recv)) / steps], device="cuda", dtype=torch.float64)
         mx = both.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)

@@ -134,7 +134,8 @@ int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const 
 /* Expert-parallel dispatch fused with the activation quantisation (no counterpart in the reference; its multi-GPU input
  * hand-off is the all-gather of prepared inputs, MOE/prepared_input.py:116-209). send_ids / send_w / send_rank describe
  * this rank's 4T pairs grouped by destination rank (b200moe_permute on the destination ranks with bm = 1: sorted_ids,
- * sorted_w, block_expert). Send row i goes to row dst_base[d] + (i - seg_start[d]) of destination d's receive buffers:
+ * sorted_w, block_expert). Send row i goes to row dst_base[d] + (i - seg_start[d]) of destination d's receive buffers
+ * (dst_base int64 [world] and seg_start int32 [world] are DEVICE arrays, so the row counts never have to reach the host):
  * peer_codes[d] u8 [capacity][3072], peer_scales[d] u8 [capacity][192] (row-major, bit-identical to b200moe_quant_mxfp4
  * of the token's row), peer_meta[d] int32 [capacity][4] = {expert id local to d, routing-weight bits, source pair
  * 4*token+slot, source rank}. Pointers are device pointers valid on this GPU (peer mappings over NVLink; this rank's own

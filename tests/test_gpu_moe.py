@@ -286,7 +286,7 @@ def test_expert_parallel_path_equals_the_layer_bit_for_bit(C, layer, tokens):
     slots = par.forward(x, logits, return_partials=True)
     ref_slots, _ = C.mxfp4_moe(x, w, router_logits=logits, return_partials=True)
     torch.cuda.synchronize()
-    assert C.last_status() == 0 and par.last_recv_rows == 4 * tokens
+    assert C.last_status() == 0 and par.recv_rows == 4 * tokens
     assert torch.equal(slots, ref_slots) and torch.equal(out, C.mxfp4_moe(x, w, router_logits=logits))
     # the combine fused into GEMM2 (result rows stored through the rank/pair tables into the owner's slot buffer)
     fused = ep.ExpertParallelMoe(w, None, routing_mode="softmax", scale=1.0, peer_pairs=4 * tokens)
