@@ -45,8 +45,10 @@ __global__ void preshuffle_shared_kernel(const uint8_t* __restrict__ codes, cons
 
 // ------------------------------------------------------------------------------------------------ activation quant
 // One 256-thread CTA per (padded) token row: bf16 -> E4M3 codes [row][6144] and the row's scales into the block's atoms.
+// With `row_scales` the scale bytes go to a row-major [tokens][192] array instead of the atoms (the prepared-input payload).
 __global__ void __launch_bounds__(256) shared_quant_kernel(const uint4* __restrict__ x, int64_t tokens, int bm_shift,
-                                                           uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms) {
+                                                           uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms,
+                                                           uint8_t* __restrict__ row_scales) {
   pdl_enter(x);
   constexpr int kIters = kH / 8 / 256;  // 3
   const int lane = threadIdx.x & 31;
@@ -90,7 +92,10 @@ __global__ void __launch_bounds__(256) shared_quant_kernel(const uint4* __restri
     uint32_t sc = static_cast<uint32_t>(e);
     sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
     sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
-    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = sc;
+    if ((lane & 15) == 0) {
+      if (row_scales != nullptr) *reinterpret_cast<uint32_t*>(row_scales + row * (kH / 32) + (idx >> 4) * 4) = sc;
+      else *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = sc;
+    }
   }
 }
 
@@ -401,8 +406,37 @@ extern "C" int b200moe_shared_quant(const void* x_bf16, int64_t tokens, int bm, 
   if (misaligned(x_bf16, 16) || misaligned(codes8, 16) || misaligned(atoms, 16)) return B200MOE_E_ALIGN;
   const int64_t rows = (tokens + bm - 1) / bm * bm;
   B200MOE_LAUNCH(shared_quant_kernel, static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream),
-                 static_cast<const uint4*>(x_bf16), tokens, shift, codes8, atoms);
+                 static_cast<const uint4*>(x_bf16), tokens, shift, codes8, atoms, static_cast<uint8_t*>(nullptr));
   return 0;
+}
+
+extern "C" int b200moe_shared_quant_rows(const void* x_bf16, int64_t tokens, uint8_t* codes8, uint8_t* scales,
+                                         void* stream) {
+  using namespace b200moe;
+  if (!x_bf16 || !codes8 || !scales || tokens < 1 || tokens > B200MOE_MAX_TOKENS) return B200MOE_E_ARG;
+  if (misaligned(x_bf16, 16) || misaligned(codes8, 16) || misaligned(scales, 4)) return B200MOE_E_ALIGN;
+  B200MOE_LAUNCH(shared_quant_kernel, static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream),
+                 static_cast<const uint4*>(x_bf16), tokens, 4, codes8, static_cast<uint8_t*>(nullptr), scales);
+  return 0;
+}
+
+static int shared_gemms(const uint8_t* w13t, const uint8_t* w2t, const uint8_t* codes8, int64_t code_rows,
+                        const b200moe::SharedWorkspace& ws, void* out_bf16, int64_t tokens, int32_t* status, void* stream) {
+  using namespace b200moe;
+  const int n_blocks = static_cast<int>(ws.rows / ws.bm);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap mx, mh;
+  int r;
+  // code_rows may be the unpadded token count: boxes that reach beyond it read zeros
+  if ((r = make_map(&mx, codes8, kH, static_cast<uint64_t>(code_rows), static_cast<uint32_t>(ws.bm)))) return r;
+  if ((r = make_map(&mh, ws.h8, kI, static_cast<uint64_t>(ws.rows), static_cast<uint32_t>(ws.bm)))) return r;
+  SharedEpilogue ep{};
+  ep.h8 = ws.h8;
+  ep.sfh8 = ws.sfh8;
+  ep.out = static_cast<__nv_bfloat16*>(out_bf16);
+  ep.tokens = tokens;
+  if ((r = launch_shared_bm<1>(ws.bm, mx, w13t, ws.sfx8, n_blocks, ep, status, st))) return r;
+  return launch_shared_bm<2>(ws.bm, mh, w2t, ws.sfh8, n_blocks, ep, status, st);
 }
 
 extern "C" int b200moe_shared_expert(const uint8_t* w13t, const uint8_t* w2t, const void* x_bf16, int64_t tokens,
@@ -415,18 +449,25 @@ extern "C" int b200moe_shared_expert(const uint8_t* w13t, const uint8_t* w2t, co
     return B200MOE_E_ALIGN;
   SharedWorkspace ws = carve_shared(static_cast<uint8_t*>(workspace), tokens);
   if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
-  int r = b200moe_shared_quant(x_bf16, tokens, ws.bm, ws.x8, ws.sfx8, stream);
+  const int r = b200moe_shared_quant(x_bf16, tokens, ws.bm, ws.x8, ws.sfx8, stream);
   if (r) return r;
-  const int n_blocks = static_cast<int>(ws.rows / ws.bm);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  CUtensorMap mx, mh;
-  if ((r = make_map(&mx, ws.x8, kH, static_cast<uint64_t>(ws.rows), static_cast<uint32_t>(ws.bm)))) return r;
-  if ((r = make_map(&mh, ws.h8, kI, static_cast<uint64_t>(ws.rows), static_cast<uint32_t>(ws.bm)))) return r;
-  SharedEpilogue ep{};
-  ep.h8 = ws.h8;
-  ep.sfh8 = ws.sfh8;
-  ep.out = static_cast<__nv_bfloat16*>(out_bf16);
-  ep.tokens = tokens;
-  if ((r = launch_shared_bm<1>(ws.bm, mx, w13t, ws.sfx8, n_blocks, ep, status, st))) return r;
-  return launch_shared_bm<2>(ws.bm, mh, w2t, ws.sfh8, n_blocks, ep, status, st);
+  return shared_gemms(w13t, w2t, ws.x8, ws.rows, ws, out_bf16, tokens, status, stream);
+}
+
+extern "C" int b200moe_scales_to_atoms(const uint8_t* rows, int64_t tokens, int cols, int bm, uint8_t* atoms, void* stream);
+
+extern "C" int b200moe_shared_expert_quantized(const uint8_t* w13t, const uint8_t* w2t, const uint8_t* codes8,
+                                               const uint8_t* scales, int64_t tokens, void* workspace,
+                                               size_t workspace_bytes, void* out_bf16, int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w13t || !w2t || !codes8 || !scales || !workspace || !out_bf16 || !status) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS) return B200MOE_E_ARG;
+  if (misaligned(workspace, 256) || misaligned(w13t, 16) || misaligned(w2t, 16) || misaligned(out_bf16, 16) ||
+      misaligned(codes8, 16) || misaligned(scales, 4))
+    return B200MOE_E_ALIGN;
+  SharedWorkspace ws = carve_shared(static_cast<uint8_t*>(workspace), tokens);
+  if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
+  const int r = b200moe_scales_to_atoms(scales, tokens, kH / 32, ws.bm, ws.sfx8, stream);
+  if (r) return r;
+  return shared_gemms(w13t, w2t, codes8, tokens, ws, out_bf16, tokens, status, stream);
 }

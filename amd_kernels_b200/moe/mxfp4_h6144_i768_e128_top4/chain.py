@@ -412,7 +412,10 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     stream; the shared expert runs on the device's side stream beside it and the current stream joins it before the
     reduce. Scratch and outputs come from ``torch.empty``."""
     if not isinstance(x, torch.Tensor):
-        raise ValueError("prepared inputs (MoeInput / MoeInputCompact) are not built")
+        from .prepared_input import MoeInput, MoeInputCompact, mxfp4_moe_prepared
+        if not isinstance(x, (MoeInput, MoeInputCompact)):
+            raise ValueError("expected BF16 [M,6144] rows, a MoeInput or a MoeInputCompact")
+        return mxfp4_moe_prepared(x, w, return_partials=return_partials)
     variant_for(x.shape[0])
     if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("expected contiguous BF16 [M,6144]")

@@ -87,6 +87,19 @@ def shared_quant(x: torch.Tensor, bm: int | None = None, *, stream=None):
     return codes, atoms
 
 
+def shared_quant_rows(x: torch.Tensor, *, stream=None):
+    """bf16 [M, 6144] -> (E4M3 codes u8 [M, 6144], E8M0 scales u8 [M, 192]) row-major: the prepared-input payload
+    (reference prepared_input.py:16-36); same bits as ``shared_quant``."""
+    _check_x(x)
+    m = x.shape[0]
+    codes = torch.empty((m, H), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((m, H // 32), dtype=torch.uint8, device=x.device)
+    st = torch.cuda.current_stream(x.device) if stream is None else stream
+    _lib.check(_lib.load().b200moe_shared_quant_rows(_ptr(x), m, _ptr(codes), _ptr(scales),
+                                                     ctypes.c_void_p(st.cuda_stream)), "shared_quant_rows")
+    return codes, scales
+
+
 def atoms_to_rows(atoms: torch.Tensor, bm: int, m: int) -> torch.Tensor:
     """Scale atoms [B, A, 512] of ``bm``-row blocks -> row-major scales [m, 4*A] (an index permutation, for checks)."""
     b, a, _ = atoms.shape
@@ -97,23 +110,38 @@ def atoms_to_rows(atoms: torch.Tensor, bm: int, m: int) -> torch.Tensor:
     return rows[:m].contiguous()
 
 
-def shared_expert(x: torch.Tensor, w: SharedWeights, *, stream=None) -> torch.Tensor:
+def shared_expert(x: torch.Tensor | None, w: SharedWeights, *, x_quant=None, stream=None) -> torch.Tensor:
     """The shared expert of bf16 ``x`` [n, 6144] -> bf16 [n, 6144] (reference shared_expert.py:70-84; served at every n
-    here). ``stream``: launch there instead of on the current stream; the buffers still come from the current stream's
+    here). ``x_quant``: ``shared_quant_rows(x)``'s (codes, scales) if already computed (then ``x`` is not read).
+    ``stream``: launch there instead of on the current stream; the buffers still come from the current stream's
     allocator pool and are recorded on ``stream``."""
     from .chain import status_word, variant_for
-    _check_x(x)
-    variant_for(x.shape[0])
     lib = _lib.load()
-    n, dev = x.shape[0], x.device
+    if x_quant is None:
+        _check_x(x)
+        n, dev = x.shape[0], x.device
+    else:
+        q, s = x_quant
+        n, dev = q.shape[0], q.device
+        if (q.shape != (n, H) or q.dtype != torch.uint8 or not q.is_contiguous() or s.shape != (n, H // 32)
+                or s.dtype != torch.uint8 or not s.is_contiguous()):
+            raise ValueError("x_quant: expected contiguous uint8 codes [M,6144] and scales [M,192]")
+    variant_for(n)
     ws_bytes = int(lib.b200moe_shared_workspace_bytes(n))
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     out = torch.empty((n, H), dtype=torch.bfloat16, device=dev)
     st = torch.cuda.current_stream(dev) if stream is None else stream
-    _lib.check(lib.b200moe_shared_expert(_ptr(w.w13), _ptr(w.w2), _ptr(x), n, _ptr(workspace), ws_bytes, _ptr(out),
-                                         _ptr(status_word(dev)), ctypes.c_void_p(st.cuda_stream)), "shared_expert")
+    if x_quant is None:
+        _lib.check(lib.b200moe_shared_expert(_ptr(w.w13), _ptr(w.w2), _ptr(x), n, _ptr(workspace), ws_bytes, _ptr(out),
+                                             _ptr(status_word(dev)), ctypes.c_void_p(st.cuda_stream)), "shared_expert")
+        used = (workspace, out, x)
+    else:
+        _lib.check(lib.b200moe_shared_expert_quantized(_ptr(w.w13), _ptr(w.w2), _ptr(q), _ptr(s), n, _ptr(workspace),
+                                                       ws_bytes, _ptr(out), _ptr(status_word(dev)),
+                                                       ctypes.c_void_p(st.cuda_stream)), "shared_expert_quantized")
+        used = (workspace, out, q, s)
     if stream is not None and stream != torch.cuda.current_stream(dev):
-        for t in (workspace, out, x):
+        for t in used:
             t.record_stream(stream)
     return out
 

@@ -230,6 +230,25 @@ size_t b200moe_shared_workspace_bytes(int64_t tokens);
 int b200moe_shared_expert(const uint8_t* w13t, const uint8_t* w2t, const void* x_bf16, int64_t tokens, void* workspace,
                           size_t workspace_bytes, void* out_bf16, int32_t* status, void* stream);
 
+/* The shared expert's input quantiser with row-major scales [T][192] (the prepared-input payload,
+ * MOE/prepared_input.py:16-36 MoeInput.shared_codes / shared_scales), and the shared expert on such pre-quantised rows
+ * (MOE/shared_expert.py:70 shared_expert(..., x_quant=)): codes8 [T][6144] need no padding rows. */
+int b200moe_shared_quant_rows(const void* x_bf16, int64_t tokens, uint8_t* codes8, uint8_t* scales, void* stream);
+int b200moe_shared_expert_quantized(const uint8_t* w13t, const uint8_t* w2t, const uint8_t* codes8, const uint8_t* scales,
+                                    int64_t tokens, void* workspace, size_t workspace_bytes, void* out_bf16,
+                                    int32_t* status, void* stream);
+/* Row-major scale bytes [T][cols] -> scale atoms [ceil(T/bm)][cols/4][512] of bm-row blocks (rows beyond T: byte 1). */
+int b200moe_scales_to_atoms(const uint8_t* rows, int64_t tokens, int cols, int bm, uint8_t* atoms, void* stream);
+
+/* ---- the compact prepared input (MOE/prepared_input.py:79-114 MoeInputCompact; MOE/sidecar_pack.py, sidecar_unpack.py;
+ * oracle MOE/reference.py:198-235 mxfp4_sidecar_pack_ref / _unpack_ref). A token's FP4 codes q4 [T][3072] are rebuilt
+ * bit for bit (signed zeros included) from its FP8 codes q8 [T][6144], both scale rows s4 / s8 [T][192] and a
+ * correction mask [T][768] (bit i%8 of byte i/8 is value i). pack writes the mask, unpack writes q4. */
+int b200moe_sidecar_pack(const uint8_t* q4, const uint8_t* s4, const uint8_t* q8, const uint8_t* s8, int64_t tokens,
+                         uint8_t* mask, void* stream);
+int b200moe_sidecar_unpack(const uint8_t* mask, const uint8_t* s4, const uint8_t* q8, const uint8_t* s8, int64_t tokens,
+                           uint8_t* q4, void* stream);
+
 /* The same reduce over slot rows that sit in another order: index int32 [T][4] gives, for pair 4*token+slot, its row in
  * rows_bf16 [N][6144] (the expert-parallel combine: rows come back from the other ranks in send order). Same arithmetic
  * and the same bits as b200moe_reduce_slots on the reordered rows. No counterpart in the reference (it has no expert

@@ -267,6 +267,38 @@ def shared_mxfp8(x: np.ndarray, w13, s13, w2, s2) -> np.ndarray:
     return (h @ dequant_shared_mxfp8(w2, s2).T).astype(np.float32)
 
 
+def _mxfp4_via_shared_codes(s4: np.ndarray, q8: np.ndarray, s8: np.ndarray):
+    """The FP4 codes (one per byte, sign in bit 3) of the FP8 values re-read at the FP4 scales, and the magnitudes they
+    were rounded from (reference.py:198-207): magnitude = |e4m3| / 2**(s4 - s8); thresholds .25 .75 1.25 1.75 2.5 3.5 5
+    with ties to the even code."""
+    ratio = np.repeat(np.exp2((s4.astype(np.int32) - s8.astype(np.int32)).astype(np.float32)), 32, axis=-1)
+    magnitude = (np.abs(e4m3_to_f32(q8)) / ratio).astype(np.float32)
+    codes = np.zeros(q8.shape, dtype=np.uint8)
+    for j, mid in enumerate((0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)):
+        codes += ((magnitude >= mid) if j % 2 else (magnitude > mid)).astype(np.uint8)
+    return codes | ((q8 >> 7) << 3), magnitude
+
+
+def sidecar_pack(q4: np.ndarray, s4: np.ndarray, q8: np.ndarray, s8: np.ndarray) -> np.ndarray:
+    """The correction mask u8 [M, K/8] (bit i % 8 is value i): set where the direct FP4 code differs from the FP4 rounding
+    of the shared FP8 code (reference.py:210-220). q4 [M, K/2] packed codes, q8 [M, K] E4M3 bytes, scales [M, K/32]."""
+    candidate, _ = _mxfp4_via_shared_codes(s4, q8, s8)
+    direct = np.stack((q4 & 15, q4 >> 4), axis=-1).reshape(q4.shape[0], -1)
+    bits = (candidate != direct).reshape(q8.shape[0], -1, 8).astype(np.uint32)
+    return (bits << np.arange(8, dtype=np.uint32)).sum(-1).astype(np.uint8)
+
+
+def sidecar_unpack(mask: np.ndarray, s4: np.ndarray, q8: np.ndarray, s8: np.ndarray) -> np.ndarray:
+    """The direct FP4 bytes [M, K/2] back from the mask (reference.py:223-235): a set bit takes the other neighbour of
+    the candidate code, the lower one when the magnitude is a midpoint that rounds up (.75, 1.75, 3.5), else the upper."""
+    candidate, magnitude = _mxfp4_via_shared_codes(s4, q8, s8)
+    bits = ((mask[..., None].astype(np.int32) >> np.arange(8)) & 1).reshape(mask.shape[0], -1).astype(bool)
+    down = (magnitude == 0.75) | (magnitude == 1.75) | (magnitude == 3.5)
+    other = (candidate & 8) | (((candidate & 7).astype(np.int32) + np.where(down, -1, 1)) & 7).astype(np.uint8)
+    codes = np.where(bits, other, candidate).astype(np.uint8)
+    return np.ascontiguousarray(codes[:, ::2] | (codes[:, 1::2] << 4))
+
+
 def make_shared_weights(seed: int = 607, hidden: int = H, inter: int = I):
     """Random MXFP8 shared-expert weights, the recipe of the reference's tests/moe/.../workload.py:48-61 with a CPU
     generator: E4M3 codes of 20*N(0,1), E8M0 bytes uniform in [118, 124)."""

@@ -13,6 +13,7 @@ Fixtures (inputs are stored or re-derivable from the stated seed; outputs come f
   reduce.npz   bf16 slots incl. signed zeros and subnormals    -> reduce_slots_bf16_ref
   moe_small.npz  E=8, H=256, I=64, T=32 MXFP4 layer            -> w4a4_moe_ref
   shared.npz   bf16 rows -> shared_mxfp8_quant_ref; seeded MXFP8 weights -> shared_mxfp8_ref; torch's E4M3 cast
+  sidecar.npz  bf16 rows -> both quantisers -> mxfp4_sidecar_pack_ref (mask) and mxfp4_sidecar_unpack_ref (== the FP4 codes)
   moe_config0.npz  the benchmark's configuration 0 (T=16, E=128, H=6144, I=768, seed 0; inputs re-derived from the seed
                by oracle.moe_oracle.make_weights / make_inputs, their CRC32 stored) -> w4a4_moe_ref on softmax top-4
                routing, and on the reference's sigmoid+bias routing
@@ -134,6 +135,20 @@ def main():
                                                                     dtype=np.uint32),
                         cast_in=(torch.randn((64, 256), generator=torch.Generator().manual_seed(3)) * 20).numpy(),
                         cast_codes=torch_codes.view(torch.uint8).numpy())
+    # ---- sidecar (compact prepared input): FP4 codes rebuilt from the shared FP8 codes + a correction mask
+    g = torch.Generator().manual_seed(33)
+    xc = (torch.randn((24, 6144), generator=g) * torch.exp2(torch.randint(-8, 9, (24, 192), generator=g).float()
+                                                            ).repeat_interleave(32, 1)).bfloat16()
+    xc[0, :64] = 0
+    xc[1, :32] = torch.tensor([0.75, 1.75, 3.5, -0.75, 0.25, 1.25, 2.5, 5.0, -0.0, 6.0, 0.5, 3.0, 448.0, -3.5, 1.0, 7.0] * 2)
+    xc[2, :32] = torch.tensor([0.75, 1.75, 3.5, -0.75, 0.25, 1.25, 2.5, 5.0] * 4) * 0.0078125
+    q4, s4 = ref.mxfp4_quant_ref(xc)
+    q8c, s8c = ref.shared_mxfp8_quant_ref(xc)
+    mask = ref.mxfp4_sidecar_pack_ref(q4, s4, q8c.view(torch.uint8), s8c)
+    back = ref.mxfp4_sidecar_unpack_ref(mask, s4, q8c.view(torch.uint8), s8c)
+    assert torch.equal(back, q4)
+    np.savez_compressed(os.path.join(HERE, "sidecar.npz"), x_bits=bits(xc), q4=q4.numpy(), s4=s4.numpy(),
+                        q8=q8c.view(torch.uint8).numpy(), s8=s8c.numpy(), mask=mask.numpy())
     print("golden fixtures written to", HERE)
 
 

@@ -121,3 +121,16 @@ def test_shared_expert_quant_cast_and_mlp_match_reference():
     out = orc.shared_mxfp8(orc.bf16_to_f32(g["x_bits"]), *weights)
     rel = np.linalg.norm(out - g["out"]) / np.linalg.norm(g["out"])
     assert rel < 2e-3, rel  # FP8 codes of h that flip on fp32 summation order
+
+
+def test_sidecar_pack_and_unpack_match_reference():
+    """mask == mxfp4_sidecar_pack_ref, and the FP4 codes come back bit for bit (reference.py:210-235)."""
+    g = golden("sidecar.npz")
+    x = orc.bf16_to_f32(g["x_bits"])
+    q4, s4 = orc.quant_mxfp4(x)
+    q8, s8 = orc.shared_mxfp8_quant(x)
+    assert (q4 == g["q4"]).all() and (s4 == g["s4"]).all() and (q8 == g["q8"]).all() and (s8 == g["s8"]).all()
+    mask = orc.sidecar_pack(q4, s4, q8, s8)
+    assert mask.shape == (x.shape[0], 768) and (mask == g["mask"]).all()
+    assert mask.any()
+    assert (orc.sidecar_unpack(mask, s4, q8, s8) == q4).all()
