@@ -198,9 +198,14 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // the expert id of a unit is fetched one unit ahead: a GEMM2 unit is only three stages long, and an L2 round trip
+      // in front of each would leave the copy queue short
+      int e_ahead = static_cast<int>(blockIdx.x) < total_units ? __ldcg(block_expert + blockIdx.x / C::kTilesM) : 0;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const int b = u / C::kTilesM, mt = u % C::kTilesM;
-        int e = __ldcg(block_expert + b);
+        int e = e_ahead;
+        const int un = u + static_cast<int>(gridDim.x);
+        if (un < total_units) e_ahead = __ldcg(block_expert + un / C::kTilesM);
         if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
           atomicExch(status, B200MOE_DEV_BAD_INDEX);
           e = 0;
@@ -607,12 +612,17 @@ __global__ void __launch_bounds__(224, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      auto block_of = [&](int u) { return u >= units1 ? (u - units1) / kW2Tiles : u / kW13Tiles; };
+      // the expert id of a unit is fetched one unit ahead (a GEMM2 unit is only three stages long)
+      int e_ahead = static_cast<int>(blockIdx.x) < total_units ? __ldcg(block_expert + block_of(blockIdx.x)) : 0;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const bool second = u >= units1;
         const int v = second ? u - units1 : u;
         const int tiles_m = second ? kW2Tiles : kW13Tiles, tiles_k = second ? kK2Tiles : kK1Tiles;
-        const int b = v / tiles_m, mt = v % tiles_m;
-        int e = __ldcg(block_expert + b);
+        const int mt = v % tiles_m;
+        int e = e_ahead;
+        const int un = u + static_cast<int>(gridDim.x);
+        if (un < total_units) e_ahead = __ldcg(block_expert + block_of(un));
         if (e < 0 || e >= num_experts) {
           atomicExch(status, B200MOE_DEV_BAD_INDEX);
           e = 0;
