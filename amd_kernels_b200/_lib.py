@@ -50,6 +50,7 @@ SIGNATURES = {
     "b200moe_reduce_slots": (c_int, [_P, _P, c_int64, _P, _P]),
     "b200moe_reduce_rows": (c_int, [_P, _P, _P, c_int64, _P, _P]),
     "b200moe_preshuffle_shared": (c_int, [_P, _P, _P, _P, _P, _P, _P]),
+    "b200moe_shared_block_rows": (c_int, [c_int64]),
     "b200moe_shared_quant": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_shared_workspace_bytes": (c_size_t, [c_int64]),
     "b200moe_shared_expert": (c_int, [_P, _P, _P, c_int64, _P, c_size_t, _P, _P, _P]),

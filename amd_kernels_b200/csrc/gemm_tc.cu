@@ -38,11 +38,16 @@ struct Cfg {
   static constexpr int kStages = BM == 128 ? (MODE == 1 ? 6 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
   // bm = 128 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
   static constexpr int kEpiGroups = kTokensAreM ? 2 : 1;
-  static constexpr int kThreads = 64 + 128 * kEpiGroups;
+  // warps: 0 = copy producer, 1 = MMA issue, 2 .. = epilogue groups, last = scale-copy issue
+  static constexpr int kThreads = 64 + 128 * kEpiGroups + 32;
+  static constexpr int kScaleWarp = 2 + 4 * kEpiGroups;
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
+  // scale columns behind the accumulators: kSfSets sets of (8 for the weight tile + 8 for the token tile), used in
+  // rotation: the scale copies are issued by their own thread, stages ahead of the MMAs that read them
+  static constexpr int kSfSets = 8;  // >= kStages: a set is reused only after the MMAs that read it have completed
   static constexpr int kSfaCol = 2 * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
-  static constexpr int kColsUsed = kSfbCol + 8;
+  static constexpr int kColsUsed = kSfaCol + 16 * kSfSets;
   static constexpr int kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
   // GEMM1 epilogue staging: up to 64 token columns x (2 groups x (32 gate + 32 up + 4 pad)) floats
   static constexpr int kEpiCols = BM < 64 ? BM : 64;
@@ -137,6 +142,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_sf[C::kStages];  // the stage's scales are in tensor memory
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -155,6 +161,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
@@ -196,8 +203,10 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      uint32_t it = 0;
       bool ok = true;
+      // slot state kept incrementally (no division in the loop): shared-memory address, barriers, phase
+      const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
+      uint32_t it = 0, slot = 0, ph = 1u, base = tiles, full = full0, empty = empty0;
       // the expert id of a unit is fetched one unit ahead: a GEMM2 unit is only three stages long, and an L2 round trip
       // in front of each would leave the copy queue short
       int e_ahead = static_cast<int>(blockIdx.x) < total_units ? __ldcg(block_expert + blockIdx.x / C::kTilesM) : 0;
@@ -212,15 +221,20 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
         }
         const uint8_t* w_src = w_tiles + static_cast<int64_t>(e * C::kTilesM + mt) * C::kTilesK * kTileRecordBytes;
         const uint8_t* sfb_src = sf_x + static_cast<int64_t>(b) * C::kActAtomsPerBlock * kAtomBytes;
+        const int row0 = b * BM;
         for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
-          const uint32_t full = smem_u32(&bar_full[s]);
-          const uint32_t base = tiles + s * C::kStageBytes;
+          if (!mbar_wait(empty, ph, abort_v, status)) { ok = false; break; }
           mbar_arrive_expect_tx(full, C::kStageBytes);
-          bulk_load(base, w_src + static_cast<int64_t>(kt) * kTileRecordBytes, kTileRecordBytes, full);
-          tma_load_2d(base + C::kBOffset, &map_x, kt * 128, b * BM, full);
-          bulk_load(base + C::kSfbOffset, sfb_src + kt * C::kSfBytes, C::kSfBytes, full);
+          bulk_load(base, w_src, kTileRecordBytes, full);
+          tma_load_2d(base + C::kBOffset, &map_x, kt * 128, row0, full);
+          bulk_load(base + C::kSfbOffset, sfb_src, C::kSfBytes, full);
+          w_src += kTileRecordBytes;
+          sfb_src += C::kSfBytes;
+          if (++slot == C::kStages) {
+            slot = 0; ph ^= 1u; base = tiles; full = full0; empty = empty0;
+          } else {
+            base += C::kStageBytes; full += 8; empty += 8;
+          }
         }
       }
       if (MODE == 1 && ok && ep.next_tiles != nullptr) {
@@ -248,39 +262,74 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BM >> 3) << 17) | (1u << 23) | (8u << 24);
-      uint32_t it = 0, ui = 0;
+      // The instruction stream of one thread bounds this kernel (every tcgen05 / mbarrier instruction costs it ~50
+      // cycles), so the per-stage work is split: the scale-copy thread (last warp) waits for the stage's bytes and copies
+      // its scales into tensor memory; this thread waits for that and issues the four MMAs. State is kept incrementally:
+      // the slot's shared-memory address >> 4 (the low word of every descriptor), its barriers, the phase, the scale set.
+      const uint32_t sf0 = smem_u32(&bar_sf[0]), empty0 = smem_u32(&bar_empty[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0, ui = 0;
+      uint32_t lo = tiles >> 4, full = sf0, empty = empty0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
         const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+        for (int kt = 0; kt < C::kTilesK; ++kt) {
+          if (!mbar_wait(full, ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t base = tiles + s * C::kStageBytes;
-          const uint32_t sfa = base + C::kABytes, sfb = base + C::kSfbOffset;
-          tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(sfa));
-          tc_cp_scales(tmem_base + C::kSfaCol + 4, scale_desc(sfa + kAtomBytes));
-          tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(sfb));
-          tc_cp_scales(tmem_base + C::kSfbCol + 4, scale_desc(sfb + kAtomBytes));
-          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // 64 elements = 32 bytes per MMA; scales: atom k/2, bytes {0,1} or {2,3} of each row's 4-byte cell
-            const uint32_t sf_id = (k & 1) * 2u;
-            const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
-            if (C::kTokensAreM)
-              tc_mma_mxf4(d_tmem, db + 2u * k, da + 2u * k, idesc, tmem_base + C::kSfbCol + 4 * (k >> 1),
-                          tmem_base + C::kSfaCol + 4 * (k >> 1), (kt | k) != 0);
-            else
-              tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
-                          tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * sfset, t_sfb = t_sfa + 8u;
+          // 64 elements = 32 bytes (descriptor + 2) per MMA; scales: atom k/2, bytes {0,1} or {2,3} of each row's cell
+          constexpr uint32_t kId0 = kIdesc, kId1 = kIdesc | (2u << 29) | (2u << 4);
+          const uint32_t w_lo = lo, x_lo = lo + (C::kBOffset >> 4);
+          if (C::kTokensAreM) {
+            tc_mma_mxf4_lo<2>(d_tmem, x_lo, w_lo, kId0, t_sfb, t_sfa, static_cast<uint32_t>(kt != 0));
+            tc_mma_mxf4_lo<1>(d_tmem, x_lo + 2, w_lo + 2, kId1, t_sfb, t_sfa);
+            tc_mma_mxf4_lo<1>(d_tmem, x_lo + 4, w_lo + 4, kId0, t_sfb + 4, t_sfa + 4);
+            tc_mma_mxf4_lo<1>(d_tmem, x_lo + 6, w_lo + 6, kId1, t_sfb + 4, t_sfa + 4);
+          } else {
+            tc_mma_mxf4_lo<2>(d_tmem, w_lo, x_lo, kId0, t_sfa, t_sfb, static_cast<uint32_t>(kt != 0));
+            tc_mma_mxf4_lo<1>(d_tmem, w_lo + 2, x_lo + 2, kId1, t_sfa, t_sfb);
+            tc_mma_mxf4_lo<1>(d_tmem, w_lo + 4, x_lo + 4, kId0, t_sfa + 4, t_sfb + 4);
+            tc_mma_mxf4_lo<1>(d_tmem, w_lo + 6, x_lo + 6, kId1, t_sfa + 4, t_sfb + 4);
           }
-          tc_commit(smem_u32(&bar_empty[s]));
+          tc_commit(empty);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == C::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; full = sf0; empty = empty0;
+          } else {
+            lo += C::kStageBytes >> 4; full += 8; empty += 8;
+          }
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+  } else if (warp == C::kScaleWarp) {
+    // ---------------------------------------------------------------- scale copies: shared memory -> tensor memory
+    if (lane == 0) {
+      const uint32_t full0 = smem_u32(&bar_full[0]), sf0 = smem_u32(&bar_sf[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0;
+      uint32_t lo = tiles >> 4, full = full0, sf = sf0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        for (int kt = 0; kt < C::kTilesK; ++kt) {
+          // full: the stage's bytes have landed, and (through the producer's wait) the MMAs that last read this slot and
+          // this scale set, kStages <= kSfSets stages ago, have completed
+          if (!mbar_wait(full, ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * sfset, t_sfb = t_sfa + 8u;
+          tc_cp_scales_lo(t_sfa, lo + (C::kABytes >> 4));
+          tc_cp_scales_lo(t_sfa + 4, lo + ((C::kABytes + kAtomBytes) >> 4));
+          tc_cp_scales_lo(t_sfb, lo + (C::kSfbOffset >> 4));
+          tc_cp_scales_lo(t_sfb + 4, lo + ((C::kSfbOffset + kAtomBytes) >> 4));
+          tc_commit(sf);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == C::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; full = full0; sf = sf0;
+          } else {
+            lo += C::kStageBytes >> 4; full += 8; sf += 8;
+          }
+        }
       }
     }
   } else {
@@ -703,17 +752,17 @@ __global__ void __launch_bounds__(224, 1)
           tc_fence_after();
           const uint32_t base = tiles + s * C::kStageBytes;
           const uint32_t sfa = base + C::kABytes, sfb = base + C::kSfbOffset;
-          tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(sfa));
-          tc_cp_scales(tmem_base + C::kSfaCol + 4, scale_desc(sfa + kAtomBytes));
-          tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(sfb));
-          tc_cp_scales(tmem_base + C::kSfbCol + 4, scale_desc(sfb + kAtomBytes));
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * (it % C::kSfSets), t_sfb = t_sfa + 8u;
+          tc_cp_scales(t_sfa, scale_desc(sfa));
+          tc_cp_scales(t_sfa + 4, scale_desc(sfa + kAtomBytes));
+          tc_cp_scales(t_sfb, scale_desc(sfb));
+          tc_cp_scales(t_sfb + 4, scale_desc(sfb + kAtomBytes));
           const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t sf_id = (k & 1) * 2u;
             const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
-            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol + 4 * (k >> 1),
-                        tmem_base + C::kSfbCol + 4 * (k >> 1), (kt | k) != 0);
+            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, t_sfa + 4 * (k >> 1), t_sfb + 4 * (k >> 1), (kt | k) != 0);
           }
           tc_commit(smem_u32(&bar_empty[s]));
         }

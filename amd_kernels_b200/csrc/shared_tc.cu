@@ -362,7 +362,7 @@ struct SharedWorkspace {
 
 static SharedWorkspace carve_shared(uint8_t* base, int64_t tokens) {
   SharedWorkspace ws{};
-  ws.bm = b200moe_block_rows(tokens);
+  ws.bm = b200moe_shared_block_rows(tokens);
   ws.rows = (tokens + ws.bm - 1) / ws.bm * ws.bm;
   const size_t blocks = static_cast<size_t>(ws.rows / ws.bm);
   size_t off = 0;
@@ -380,6 +380,13 @@ static SharedWorkspace carve_shared(uint8_t* base, int64_t tokens) {
 }
 
 }  // namespace b200moe
+
+// Dense blocks: the widest block that the token count fills, so the 14 MB of weights are streamed as few times as
+// possible (once up to 128 tokens) and the few CTAs this takes leave the other SMs to the routed experts' kernels.
+extern "C" int b200moe_shared_block_rows(int64_t tokens) {
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS) return 0;
+  return tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
+}
 
 extern "C" int b200moe_preshuffle_shared(const uint8_t* w13, const uint8_t* s13, const uint8_t* w2, const uint8_t* s2,
                                          uint8_t* w13t, uint8_t* w2t, void* stream) {

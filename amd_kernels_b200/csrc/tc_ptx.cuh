@@ -136,6 +136,36 @@ __device__ __forceinline__ void tc_mma_mxf8(uint32_t d, uint64_t a, uint64_t b, 
       : "memory");
 }
 
+// Lean forms for the MMA-issuing thread, whose instruction stream bounds the kernel: descriptors are passed as their low
+// 32-bit word (shared-memory address >> 4; the tiles sit below 256 KB, so it fits 14 bits) and the constant high word is
+// an immediate, so no 64-bit arithmetic is left in the loop.
+constexpr uint32_t kOperandDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version bit 46, 128B swizzle
+constexpr uint32_t kScaleDescHi = (128u >> 4) | (1u << 14);                  // SBO 128 B, version bit 46, no swizzle
+
+__device__ __forceinline__ void tc_cp_scales_lo(uint32_t taddr, uint32_t desc_lo) {
+  asm volatile("{\n.reg .b64 d;\nmov.b64 d, {%1, %2};\ntcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n}\n" ::"r"(taddr),
+               "r"(desc_lo), "n"(kScaleDescHi)
+               : "memory");
+}
+// ACC: 1 = accumulate, 0 = overwrite, 2 = take it from `accumulate`
+template <int ACC>
+__device__ __forceinline__ void tc_mma_mxf4_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
+                                               uint32_t sfb, uint32_t accumulate = 1u) {
+  if (ACC == 2) {
+    asm volatile(
+        "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %7};\nmov.b64 db, {%2, %7};\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate), "n"(kOperandDescHi)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %6};\nmov.b64 db, {%2, %6};\nsetp.ne.b32 p, %7, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "n"(kOperandDescHi), "n"(ACC)
+        : "memory");
+  }
+}
+
 // two E4M3 codes: `lo` in the low byte, `hi` in the high byte; round to nearest even, saturating
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   uint16_t out;

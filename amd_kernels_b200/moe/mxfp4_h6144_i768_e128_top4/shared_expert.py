@@ -77,7 +77,7 @@ def shared_quant(x: torch.Tensor, bm: int | None = None, *, stream=None):
     _check_x(x)
     lib = _lib.load()
     m = x.shape[0]
-    bm = int(lib.b200moe_block_rows(m)) if bm is None else bm
+    bm = int(lib.b200moe_shared_block_rows(m)) if bm is None else bm
     rows = (m + bm - 1) // bm * bm
     codes = torch.empty((rows, H), dtype=torch.uint8, device=x.device)
     atoms = torch.empty((rows // bm, H // 128, 512), dtype=torch.uint8, device=x.device)

@@ -217,6 +217,9 @@ int b200moe_preshuffle_shared(const uint8_t* w13, const uint8_t* w13_scale, cons
 #define B200MOE_SHARED_W13T_BYTES (12 * 48 * 17408)
 #define B200MOE_SHARED_W2T_BYTES (48 * 6 * 17408)
 
+/* The dense block height the shared expert uses at T tokens: 16 / 32 / 64 up to that many tokens, else 128. */
+int b200moe_shared_block_rows(int64_t tokens);
+
 /* Input quantiser of the shared expert (MOE/reference.py:162-171 shared_mxfp8_quant_ref: scale = ceil_pow2(amax/448),
  * exponent byte >= 1, round to nearest even), bit-exact. x bf16 [T][6144] -> codes8 [ceil(T/bm)*bm][6144] (padding
  * rows zero) and scale atoms [ceil(T/bm)][48][512]: row r of a block keeps scale j of K-tile a at byte
