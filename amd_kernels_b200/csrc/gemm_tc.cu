@@ -589,7 +589,7 @@ __device__ __forceinline__ bool wait_count(const int32_t* counter, int target, v
 }
 
 template <int BM>
-__global__ void __launch_bounds__(224, 1)
+__global__ void __launch_bounds__(256, 1)
     gemm12_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_h,
                   const uint8_t* __restrict__ w13t, const uint8_t* __restrict__ w2t, const uint8_t* __restrict__ sf_x,
                   const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid, EpilogueArgs ep,
@@ -600,6 +600,7 @@ __global__ void __launch_bounds__(224, 1)
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[CC::kStages];
   __shared__ __align__(8) uint64_t bar_empty[CC::kStages];
+  __shared__ __align__(8) uint64_t bar_sf[CC::kStages];  // the stage's scales are in tensor memory (warp 7 copies them)
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -617,6 +618,7 @@ __global__ void __launch_bounds__(224, 1)
     for (int s = 0; s < CC::kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
@@ -738,7 +740,11 @@ __global__ void __launch_bounds__(224, 1)
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BM >> 3) << 17) | (1u << 23) | (8u << 24);
-      uint32_t it = 0, ui = 0;
+      constexpr uint32_t kId0 = kIdesc, kId1 = kIdesc | (2u << 29) | (2u << 4);
+      // as in grouped_gemm_kernel: warp 7 copies the scales, this thread waits for that and issues the MMAs
+      const uint32_t sf0 = smem_u32(&bar_sf[0]), empty0 = smem_u32(&bar_empty[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0, ui = 0;
+      uint32_t lo = tiles >> 4, sf = sf0, empty = empty0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
         const int tiles_k = u >= units1 ? kK2Tiles : kK1Tiles;
@@ -746,27 +752,51 @@ __global__ void __launch_bounds__(224, 1)
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
-        for (int kt = 0; kt < tiles_k; ++kt, ++it) {
-          const uint32_t s = it % CC::kStages, ph = (it / CC::kStages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+        for (int kt = 0; kt < tiles_k; ++kt) {
+          if (!mbar_wait(sf, ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t base = tiles + s * C::kStageBytes;
-          const uint32_t sfa = base + C::kABytes, sfb = base + C::kSfbOffset;
-          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * (it % C::kSfSets), t_sfb = t_sfa + 8u;
-          tc_cp_scales(t_sfa, scale_desc(sfa));
-          tc_cp_scales(t_sfa + 4, scale_desc(sfa + kAtomBytes));
-          tc_cp_scales(t_sfb, scale_desc(sfb));
-          tc_cp_scales(t_sfb + 4, scale_desc(sfb + kAtomBytes));
-          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t sf_id = (k & 1) * 2u;
-            const uint32_t idesc = kIdesc | (sf_id << 29) | (sf_id << 4);
-            tc_mma_mxf4(d_tmem, da + 2u * k, db + 2u * k, idesc, t_sfa + 4 * (k >> 1), t_sfb + 4 * (k >> 1), (kt | k) != 0);
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * sfset, t_sfb = t_sfa + 8u;
+          const uint32_t w_lo = lo, x_lo = lo + (C::kBOffset >> 4);
+          tc_mma_mxf4_lo<2>(d_tmem, w_lo, x_lo, kId0, t_sfa, t_sfb, static_cast<uint32_t>(kt != 0));
+          tc_mma_mxf4_lo<1>(d_tmem, w_lo + 2, x_lo + 2, kId1, t_sfa, t_sfb);
+          tc_mma_mxf4_lo<1>(d_tmem, w_lo + 4, x_lo + 4, kId0, t_sfa + 4, t_sfb + 4);
+          tc_mma_mxf4_lo<1>(d_tmem, w_lo + 6, x_lo + 6, kId1, t_sfa + 4, t_sfb + 4);
+          tc_commit(empty);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == CC::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; sf = sf0; empty = empty0;
+          } else {
+            lo += C::kStageBytes >> 4; sf += 8; empty += 8;
           }
-          tc_commit(smem_u32(&bar_empty[s]));
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+  } else if (warp == 7) {
+    // ---------------------------------------------------------------- scale copies: shared memory -> tensor memory
+    if (lane == 0) {
+      const uint32_t full0 = smem_u32(&bar_full[0]), sf0 = smem_u32(&bar_sf[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0;
+      uint32_t lo = tiles >> 4, full = full0, sf = sf0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const int tiles_k = u >= units1 ? kK2Tiles : kK1Tiles;
+        for (int kt = 0; kt < tiles_k; ++kt) {
+          if (!mbar_wait(full, ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 16u * sfset, t_sfb = t_sfa + 8u;
+          tc_cp_scales_lo(t_sfa, lo + (C::kABytes >> 4));
+          tc_cp_scales_lo(t_sfa + 4, lo + ((C::kABytes + kAtomBytes) >> 4));
+          tc_cp_scales_lo(t_sfb, lo + (C::kSfbOffset >> 4));
+          tc_cp_scales_lo(t_sfb + 4, lo + ((C::kSfbOffset + kAtomBytes) >> 4));
+          tc_commit(sf);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == CC::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; full = full0; sf = sf0;
+          } else {
+            lo += C::kStageBytes >> 4; full += 8; sf += 8;
+          }
+        }
       }
     }
   } else if (warp < 6) {
@@ -955,7 +985,7 @@ static int launch12(const CUtensorMap& mx, const CUtensorMap& mh, const uint8_t*
   const int64_t max_units = max_rows / BM * (kW13Tiles + kW2Tiles);
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   if (grid <= 0) return 0;
-  B200MOE_LAUNCH((gemm12_kernel<BM>), grid, 224, CC::kSmemBytes, stream, mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep,
+  B200MOE_LAUNCH((gemm12_kernel<BM>), grid, 256, CC::kSmemBytes, stream, mx, mh, w13t, w2t, sfx, block_expert, num_valid, ep,
                  done, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
