@@ -109,9 +109,11 @@ struct Cfg8 {
   static constexpr int kStageBytes = kSfbOffset + 1024;
   static constexpr int kTxBytes = kTileRecordBytes + BM * 128 + kAtomBytes;
   static constexpr int kStages = BM == 128 ? 5 : (BM == 64 ? 6 : 8);
+  // scale columns behind the accumulators: 8 sets of (4 weight + 4 token columns) used in rotation; their copies are
+  // issued by a thread of their own (warp 6), stages ahead of the MMAs
+  static constexpr int kSfSets = 8;
   static constexpr int kSfaCol = 2 * BM;
-  static constexpr int kSfbCol = kSfaCol + 4;
-  static constexpr int kColsUsed = kSfbCol + 4;
+  static constexpr int kColsUsed = kSfaCol + 8 * kSfSets;
   static constexpr int kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
   static constexpr int kEpiCols = MODE == 1 ? (BM < 64 ? BM : 64) : (BM < 32 ? BM : 32);
   static constexpr int kEpiRowFloats = MODE == 1 ? 136 : 132;
@@ -128,13 +130,14 @@ struct SharedEpilogue {
 };
 
 template <int MODE, int BM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(224, 1)
     shared_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                        const uint8_t* __restrict__ sf_x, int n_blocks, SharedEpilogue ep, int32_t* status) {
   using C = Cfg8<MODE, BM>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_sf[C::kStages];
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(192, 1)
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
@@ -202,33 +206,59 @@ __global__ void __launch_bounds__(192, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ------------------------------------------------ MMA issue
-      // E4M3 x E4M3 (format 0), UE8M0 scales, M = 128, N = BM
+      // E4M3 x E4M3 (format 0), UE8M0 scales, M = 128, N = BM; scale byte k of each row's 4-byte cell for MMA k
       constexpr uint32_t kIdesc = (static_cast<uint32_t>(BM >> 3) << 17) | (1u << 23) | (8u << 24);
-      uint32_t it = 0, ui = 0;
+      const uint32_t sf0 = smem_u32(&bar_sf[0]), empty0 = smem_u32(&bar_empty[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0, ui = 0;
+      uint32_t lo = tiles >> 4, sf = sf0, empty = empty0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
         const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BM;
-        for (int kt = 0; kt < C::kTilesK; ++kt, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+        for (int kt = 0; kt < C::kTilesK; ++kt) {
+          if (!mbar_wait(sf, ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t base = tiles + s * C::kStageBytes;
-          tc_cp_scales(tmem_base + C::kSfaCol, scale_desc(base + 128 * 128));
-          tc_cp_scales(tmem_base + C::kSfbCol, scale_desc(base + C::kSfbOffset));
-          const uint64_t da = operand_desc(base), db = operand_desc(base + C::kBOffset);
-#pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            // 32 elements = 32 bytes per MMA; scale byte k of each row's 4-byte cell
-            const uint32_t idesc = kIdesc | (k << 29) | (k << 4);
-            tc_mma_mxf8(d_tmem, da + 2u * k, db + 2u * k, idesc, tmem_base + C::kSfaCol, tmem_base + C::kSfbCol,
-                        (kt | k) != 0);
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 8u * sfset, t_sfb = t_sfa + 4u;
+          const uint32_t w_lo = lo, x_lo = lo + (C::kBOffset >> 4);
+          // 32 elements = 32 bytes (descriptor + 2) per MMA
+          tc_mma_mxf8_lo<2>(d_tmem, w_lo, x_lo, kIdesc, t_sfa, t_sfb, static_cast<uint32_t>(kt != 0));
+          tc_mma_mxf8_lo<1>(d_tmem, w_lo + 2, x_lo + 2, kIdesc | (1u << 29) | (1u << 4), t_sfa, t_sfb);
+          tc_mma_mxf8_lo<1>(d_tmem, w_lo + 4, x_lo + 4, kIdesc | (2u << 29) | (2u << 4), t_sfa, t_sfb);
+          tc_mma_mxf8_lo<1>(d_tmem, w_lo + 6, x_lo + 6, kIdesc | (3u << 29) | (3u << 4), t_sfa, t_sfb);
+          tc_commit(empty);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == C::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; sf = sf0; empty = empty0;
+          } else {
+            lo += C::kStageBytes >> 4; sf += 8; empty += 8;
           }
-          tc_commit(smem_u32(&bar_empty[s]));
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+  } else if (warp == 6) {
+    if (lane == 0) {  // ------------------------------------------------ scale copies: shared memory -> tensor memory
+      const uint32_t full0 = smem_u32(&bar_full[0]), sf0 = smem_u32(&bar_sf[0]);
+      uint32_t slot = 0, ph = 0, sfset = 0;
+      uint32_t lo = tiles >> 4, full = full0, sf = sf0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        for (int kt = 0; kt < C::kTilesK; ++kt) {
+          if (!mbar_wait(full, ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_sfa = tmem_base + C::kSfaCol + 8u * sfset;
+          tc_cp_scales_lo(t_sfa, lo + ((128 * 128) >> 4));
+          tc_cp_scales_lo(t_sfa + 4, lo + (C::kSfbOffset >> 4));
+          tc_commit(sf);
+          sfset = (sfset + 1u) & (C::kSfSets - 1);
+          if (++slot == C::kStages) {
+            slot = 0; ph ^= 1u; lo = tiles >> 4; full = full0; sf = sf0;
+          } else {
+            lo += C::kStageBytes >> 4; full += 8; sf += 8;
+          }
+        }
       }
     }
   } else {
@@ -335,7 +365,7 @@ static int launch_shared(const CUtensorMap& mx, const uint8_t* w_tiles, const ui
   const int units = n_blocks * C::kTilesM;
   const int grid = units < sm_count() ? units : sm_count();
   if (grid <= 0) return 0;
-  B200MOE_LAUNCH((shared_gemm_kernel<MODE, BM>), grid, 192, C::kSmemBytes, stream, mx, w_tiles, sf_x, n_blocks, ep, status);
+  B200MOE_LAUNCH((shared_gemm_kernel<MODE, BM>), grid, 224, C::kSmemBytes, stream, mx, w_tiles, sf_x, n_blocks, ep, status);
   return 0;
 }
 

@@ -166,6 +166,24 @@ __device__ __forceinline__ void tc_mma_mxf4_lo(uint32_t d, uint32_t a_lo, uint32
   }
 }
 
+template <int ACC>
+__device__ __forceinline__ void tc_mma_mxf8_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
+                                               uint32_t sfb, uint32_t accumulate = 1u) {
+  if (ACC == 2) {
+    asm volatile(
+        "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %7};\nmov.b64 db, {%2, %7};\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate), "n"(kOperandDescHi)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %6};\nmov.b64 db, {%2, %6};\nsetp.ne.b32 p, %7, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "n"(kOperandDescHi), "n"(ACC)
+        : "memory");
+  }
+}
+
 // two E4M3 codes: `lo` in the low byte, `hi` in the high byte; round to nearest even, saturating
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   uint16_t out;
