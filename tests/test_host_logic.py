@@ -40,6 +40,10 @@ def test_sizes_match_oracle_and_reference_bounds():
         assert lib.b200moe_workspace_bytes(tokens, 128) > tokens * 3264
     assert [lib.b200moe_block_rows(t) for t in (1, 256, 257, 896, 897, 1536, 1537, 87381)] == [16, 16, 32, 32, 64, 64, 128, 128]
     assert lib.b200moe_workspace_bytes(0, 128) == 0 and lib.b200moe_workspace_bytes(87382, 128) == 0
+    # the shared expert's dense blocks: the widest block the token count fills
+    assert [lib.b200moe_shared_block_rows(t) for t in (1, 16, 17, 32, 33, 64, 65, 87381)] == [16, 16, 32, 32, 64, 64, 128, 128]
+    assert lib.b200moe_shared_block_rows(0) == 0 and lib.b200moe_shared_workspace_bytes(0) == 0
+    assert lib.b200moe_shared_workspace_bytes(100) >= 128 * (6144 + 768)
     assert lib.b200moe_permute_scratch_bytes(256, 128) == 0 and lib.b200moe_permute_scratch_bytes(257, 128) == 2 * 128 * 4
 
 
