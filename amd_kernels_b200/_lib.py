@@ -59,6 +59,7 @@ SIGNATURES = {
     "b200moe_scales_to_atoms": (c_int, [_P, c_int64, c_int, c_int, _P, _P]),
     "b200moe_sidecar_pack": (c_int, [_P, _P, _P, _P, c_int64, _P, _P]),
     "b200moe_sidecar_unpack": (c_int, [_P, _P, _P, _P, c_int64, _P, _P]),
+    "b200moe_router_gemm_quant": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
     "b200moe_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_forward": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, c_size_t, _P, _P, _P, _P]),
     "b200moe_forward_host": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, _P, _P, c_size_t, _P, _P, _P, _P, _P]),

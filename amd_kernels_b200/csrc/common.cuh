@@ -109,6 +109,21 @@ __device__ __forceinline__ uint32_t e2m1_code(float v, int e) {
   return c | ((__float_as_uint(v) >> 31) << 3);
 }
 
+// ceil_pow2(amax / 448) as an E8M0 byte, at least 1 (the reference's shared_mxfp8_quant_ref)
+__device__ __forceinline__ int mxfp8_scale(float amax) {
+  const uint32_t u = __float_as_uint(__fdiv_rn(amax, 448.0f));
+  int e = static_cast<int>((u >> 23) & 255u);
+  if ((u & 0x7fffffu) != 0u && e < 255) ++e;
+  return e < 1 ? 1 : e;
+}
+
+// two E4M3 codes: `lo` in the low byte, `hi` in the high byte; round to nearest even, saturating
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  uint16_t out;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(out) : "f"(hi), "f"(lo));
+  return out;
+}
+
 // two E2M1 codes in one byte: `lo` in the low nibble, `hi` in the high nibble; round to nearest even, saturating.
 // Same codes as e2m1_code on a value already divided by the block scale (ties go to the even code, -0 keeps its sign).
 __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {

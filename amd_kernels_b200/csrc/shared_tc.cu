@@ -13,14 +13,6 @@ namespace b200moe {
 constexpr int kS1TilesK = kH / 128;  // 48 K-tiles of 128 elements in the first GEMM
 constexpr int kS2TilesK = kI / 128;  // 6 in the second
 
-// ceil_pow2(amax / 448) as an E8M0 byte, at least 1 (the reference's shared_mxfp8_quant_ref)
-__device__ __forceinline__ int mxfp8_scale(float amax) {
-  const uint32_t u = __float_as_uint(__fdiv_rn(amax, 448.0f));
-  int e = static_cast<int>((u >> 23) & 255u);
-  if ((u & 0x7fffffu) != 0u && e < 255) ++e;
-  return e < 1 ? 1 : e;
-}
-
 // ------------------------------------------------------------------------------------------------ weight preshuffle
 template <int K_BYTES, int TILES_M, bool IS_W13>
 __global__ void preshuffle_shared_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,

@@ -184,11 +184,6 @@ __device__ __forceinline__ void tc_mma_mxf8_lo(uint32_t d, uint32_t a_lo, uint32
   }
 }
 
-// two E4M3 codes: `lo` in the low byte, `hi` in the high byte; round to nearest even, saturating
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
-  uint16_t out;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(out) : "f"(hi), "f"(lo));
-  return out;
-}
+
 
 }  // namespace b200moe

@@ -385,6 +385,27 @@ def router_gemm_partials(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return parts.permute(1, 0, 2)
 
 
+def router_gemm_quant(x: torch.Tensor, gate: torch.Tensor, shared: bool = False):
+    """One pass over bf16 x [M, 6144]: the split-K logit partials of ``router_gemm_partials``, the row-major MXFP4 operands
+    of ``mxfp4_quant`` and, with ``shared``, the row-major MXFP8 operands of ``shared_quant_rows`` (else None), all with
+    those kernels' bits (reference router_mxfp4_mxfp8_quant_row_scales.py)."""
+    if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("expected contiguous BF16 [M,6144]")
+    if gate.dtype != torch.float32 or gate.ndim != 2 or gate.shape[1] != H or not gate.is_contiguous():
+        raise ValueError("expected a contiguous fp32 gate [E, 6144]")
+    lib = _lib.load()
+    m, n_exp, dev = x.shape[0], gate.shape[0], x.device
+    splits = int(lib.b200moe_router_splits(m))
+    parts = torch.empty((splits, m, n_exp), dtype=torch.float32, device=dev)
+    q4 = torch.empty((m, H // 2), dtype=torch.uint8, device=dev)
+    s4 = torch.empty((m, H // 32), dtype=torch.uint8, device=dev)
+    q8 = torch.empty((m, H), dtype=torch.uint8, device=dev) if shared else None
+    s8 = torch.empty((m, H // 32), dtype=torch.uint8, device=dev) if shared else None
+    _lib.check(lib.b200moe_router_gemm_quant(_ptr(x), _ptr(gate), m, n_exp, splits, _ptr(parts), _ptr(q4), _ptr(s4),
+                                             _ptr(q8), _ptr(s8), _stream(dev)), "router_gemm_quant")
+    return parts.permute(1, 0, 2), (q4, s4), (q8, s8)
+
+
 def route(x, w, router_logits=None):
     """The entry's routing (topk weights incl. the routed scale, topk ids), exposed for numerical checks
     (reference chain.py:106-110)."""

@@ -74,6 +74,15 @@ int b200moe_router_splits(int64_t tokens);
 int b200moe_router_gemm(const void* x_bf16, const float* gate, int64_t tokens, int num_experts, int splits,
                         float* partials, void* stream);
 
+/* The router GEMM fused with the input quantisers: one pass over x writes the split-K partials as above and, row-major,
+ * the routed experts' MXFP4 operands (codes4 [T][3072], scales4 [T][192], the bits of b200moe_quant_mxfp4) and, when
+ * codes8 / scales8 are given, the shared expert's MXFP8 operands ([T][6144], [T][192], the bits of
+ * b200moe_shared_quant_rows) (MOE/router_mxfp4_quant_line_layout.py:48-400,
+ * MOE/router_mxfp4_mxfp8_quant_row_scales.py router_mxfp4_mxfp8_quant_row_scales). */
+int b200moe_router_gemm_quant(const void* x_bf16, const float* gate, int64_t tokens, int num_experts, int splits,
+                              float* partials, uint8_t* codes4, uint8_t* scales4, uint8_t* codes8, uint8_t* scales8,
+                              void* stream);
+
 /* Router top-4 (MOE/router_topk.py:239-272 splitk_biased_topk). logits[t][e] = sum over s<S of
  * partials[t*stride_t + s*stride_s + e], added from 0.0 in split order; plain logits are S=1. mode SIGMOID_BIAS:
  * s = sigmoid(logit), choice = s + bias[e], weight = s*scale / sum of the 4 chosen s. mode SOFTMAX: choice = logit,

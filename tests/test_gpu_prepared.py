@@ -109,3 +109,17 @@ def test_gather_on_one_rank_and_argument_errors(P, full_layer):
     routed_only = C.MoeWeights(None, None, w.w13, None, w.w2, None)
     with pytest.raises(ValueError):
         P.prepare_mxfp4_moe(x, routed_only)
+
+
+@pytest.mark.parametrize("m", [1, 17, 300, 2100])
+def test_router_gemm_fused_with_the_quantisers(full_layer, m):
+    """One pass over x gives the router GEMM's partials and both quantisers' payloads, bit for bit."""
+    C, S, w = full_layer
+    x = rows(m, 60 + m).cuda()
+    parts, (q4, s4), (q8, s8) = C.router_gemm_quant(x, w.router_weight, shared=True)
+    assert torch.equal(parts, C.router_gemm_partials(x, w.router_weight))
+    want4, want8 = C.mxfp4_quant(x), S.shared_quant_rows(x)
+    assert torch.equal(q4, want4[0]) and torch.equal(s4, want4[1])
+    assert torch.equal(q8, want8[0]) and torch.equal(s8, want8[1])
+    _, _, (n8, ns8) = C.router_gemm_quant(x, w.router_weight)
+    assert n8 is None and ns8 is None
