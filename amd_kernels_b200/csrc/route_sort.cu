@@ -314,9 +314,9 @@ extern "C" int64_t b200moe_max_sorted_rows(int64_t tokens, int bm, int num_exper
 }
 
 extern "C" int b200moe_block_rows(int64_t tokens) {
-  if (tokens <= 256) return 16;
-  if (tokens <= 896) return 32;
-  if (tokens <= 1536) return 64;
+  if (tokens <= 480) return 16;
+  if (tokens <= 1024) return 32;
+  if (tokens <= 1728) return 64;
   return 128;
 }
 
