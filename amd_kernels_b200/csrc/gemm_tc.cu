@@ -5,9 +5,13 @@
 // operand. So one pass over an expert's weights serves its whole block, the accumulator of output feature i sits in TMEM
 // lane i, and a token is a TMEM column.
 //
-//   warp 0    producer: one thread issues TMA tile loads (128B-swizzled FP4 tiles) and bulk copies of scale atoms
-//   warp 1    MMA: allocates TMEM; one thread copies scale atoms to TMEM (tcgen05.cp) and issues tcgen05.mma
-//   (the one-launch kernel gemm12_kernel adds warp 6: a second producer for the token-side operand)
+//   warp 0    producer: one thread issues the bulk copies of weight tile records and scale atoms and the TMA tile loads of
+//             the token codes
+//   warp 1    MMA: allocates TMEM; one thread issues tcgen05.mma, four per stage
+//   last warp scale copies: one thread moves each stage's scale atoms into TMEM (tcgen05.cp), stages ahead of the MMAs.
+//             Two issuing threads because every tcgen05 / mbarrier instruction costs its thread ~50 cycles whatever the
+//             size of the MMA, and one thread doing both was what bounded the kernel
+//   (the one-launch kernel gemm12_kernel also has warp 6: a second producer for the token-side operand)
 //   warps 2-5 epilogue (bm = 128: a second group, warps 6-9, takes every other unit): tcgen05.ld of the accumulator, then
 //             GEMM1: SwiGLU-OAI (gate and up rows of one tile live in neighbouring lane quarters), MXFP4 requantisation
 //                    of 32 intermediate columns = the 32 lanes of a warp, codes and scale atoms to global memory

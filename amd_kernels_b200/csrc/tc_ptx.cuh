@@ -70,17 +70,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
-}
-__device__ __forceinline__ void tc_mma_mxf4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-      : "memory");
-}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -115,30 +104,11 @@ __device__ __forceinline__ bool epilogue_all(bool ok, uint32_t barrier_id) {
   return out != 0;
 }
 
-// K-major operand tile in shared memory, 128-byte rows, 128B swizzle: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
-  return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// One 512-byte scale atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
-  return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
-}
-
-
-// block-scaled FP8 (E4M3 x E4M3, one UE8M0 scale per 32 elements): M = 128, K = 32 per instruction
-__device__ __forceinline__ void tc_mma_mxf8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::"r"(d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-      : "memory");
-}
-
-// Lean forms for the MMA-issuing thread, whose instruction stream bounds the kernel: descriptors are passed as their low
-// 32-bit word (shared-memory address >> 4; the tiles sit below 256 KB, so it fits 14 bits) and the constant high word is
-// an immediate, so no 64-bit arithmetic is left in the loop.
+// Shared-memory descriptors are passed as their low 32-bit word (shared-memory address >> 4; the tiles sit below 256 KB,
+// so it fits 14 bits) and the constant high word is an immediate: the instruction stream of the issuing threads bounds
+// the kernels, so no 64-bit arithmetic is left in their loops. Operand tiles are K-major with 128-byte rows and the
+// 128-byte swizzle (8-row groups 1024 bytes apart); a scale atom is 32 rows of 16 bytes, no swizzle (8-row groups 128
+// bytes apart).
 constexpr uint32_t kOperandDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version bit 46, 128B swizzle
 constexpr uint32_t kScaleDescHi = (128u >> 4) | (1u << 14);                  // SBO 128 B, version bit 46, no swizzle
 
@@ -166,6 +136,7 @@ __device__ __forceinline__ void tc_mma_mxf4_lo(uint32_t d, uint32_t a_lo, uint32
   }
 }
 
+// block-scaled FP8 (E4M3 x E4M3, one UE8M0 scale per 32 elements): M = 128, K = 32 per instruction
 template <int ACC>
 __device__ __forceinline__ void tc_mma_mxf8_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
                                                uint32_t sfb, uint32_t accumulate = 1u) {
