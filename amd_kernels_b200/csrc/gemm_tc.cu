@@ -39,17 +39,23 @@ struct Cfg {
   // bm = 128 (prefill): the token block is the 128-row M operand and the weight tile is N, so a TMEM lane is a token and
   // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
   static constexpr bool kTokensAreM = BM == 128;
-  static constexpr int kStages = BM == 128 ? (MODE == 1 ? 6 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
-  // bm = 128 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
-  static constexpr int kEpiGroups = kTokensAreM ? 2 : 1;
+  // GEMM1 at bm = 128 is bound by what its issuing threads can issue, so it runs TWO CTAs per SM, each with half the
+  // pipeline (3 stages), one accumulator buffer and one epilogue group: two independent instruction streams feed the
+  // tensor pipe, and one CTA's epilogue overlaps the other's MMAs.
+  static constexpr int kCtasPerSm = (MODE == 1 && BM == 128) ? 2 : 1;
+  static constexpr int kAccBufs = kCtasPerSm == 2 ? 1 : 2;
+  static constexpr int kStages = BM == 128 ? (MODE == 1 ? 3 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
+  // bm = 128 GEMM2 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
+  static constexpr int kEpiGroups = (kTokensAreM && kAccBufs == 2) ? 2 : 1;
   // warps: 0 = copy producer, 1 = MMA issue, 2 .. = epilogue groups, last = scale-copy issue
   static constexpr int kThreads = 64 + 128 * kEpiGroups + 32;
   static constexpr int kScaleWarp = 2 + 4 * kEpiGroups;
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   // scale columns behind the accumulators: kSfSets sets of (8 for the weight tile + 8 for the token tile), used in
   // rotation: the scale copies are issued by their own thread, stages ahead of the MMAs that read them
-  static constexpr int kSfSets = 8;  // >= kStages: a set is reused only after the MMAs that read it have completed
-  static constexpr int kSfaCol = 2 * kAccCols;
+  static constexpr int kSfSets = kCtasPerSm == 2 ? 4 : 8;  // >= kStages: a set is reused only after its MMAs completed
+  static_assert(kSfSets >= kStages, "scale sets");
+  static constexpr int kSfaCol = kAccBufs * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
   static constexpr int kColsUsed = kSfaCol + 16 * kSfSets;
   static constexpr int kTmemCols = kColsUsed <= 64 ? 64 : (kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512));
@@ -137,7 +143,7 @@ __device__ __forceinline__ RowPlacer make_placer(const EpilogueArgs& ep, __nv_bf
 }
 
 template <int MODE, int BM>
-__global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
+__global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), (Cfg<MODE, BM>::kCtasPerSm))
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                         const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
                         const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status, int num_experts,
@@ -275,7 +281,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
       uint32_t lo = tiles >> 4, full = sf0, empty = empty0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-        const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+        const uint32_t acc = ui % C::kAccBufs, aph = (ui / C::kAccBufs) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
@@ -350,7 +356,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       if (C::kEpiGroups == 2 && static_cast<int>(ui & 1u) != group) continue;  // group g owns accumulator buffer g
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
-      const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
+      const uint32_t acc = ui % C::kAccBufs, aph = (ui / C::kAccBufs) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
       __nv_bfloat16* my_dst = nullptr;
       float my_wt = 0.0f;
@@ -949,13 +955,19 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
   using C = Cfg<MODE, BM>;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
+    if (C::kCtasPerSm > 1) {  // two CTAs need the whole shared-memory carve-out of the SM
+      e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
     configured = true;
   }
   const int64_t max_units = max_rows / BM * C::kTilesM;
-  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  const int64_t ctas = static_cast<int64_t>(sm_count()) * C::kCtasPerSm;
+  const int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
   if (grid <= 0) return 0;
   B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
