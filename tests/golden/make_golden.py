@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by running the reference's own torch oracle.
 
-Run once in the build container, where the reference checkout is mounted (pass its root as argv[1], default
-``/root/reference``):  ``python tests/golden/make_golden.py [REFERENCE_ROOT]``.  The GPU box has no reference checkout;
-tests read only the ``.npz`` files written here. ``reference.py`` is loaded by file path because the package's
+Run once where a checkout of the reference project is available (pass its root as argv[1] or in the environment variable
+``AMD_KERNELS_REFERENCE``):  ``python tests/golden/make_golden.py REFERENCE_ROOT``.  Machines that run the tests need no
+reference checkout; tests read only the ``.npz`` files written here. ``reference.py`` is loaded by file path because the package's
 ``__init__`` imports the AMD JIT toolchain.
 
 Fixtures (inputs are stored or re-derivable from the stated seed; outputs come from the reference functions named):
@@ -44,7 +44,10 @@ def bits(t):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AMD_KERNELS_REFERENCE")
+    if not root:
+        raise SystemExit("usage: make_golden.py REFERENCE_ROOT (or set AMD_KERNELS_REFERENCE)")
+    ref = load_reference(root)
     torch.set_num_threads(os.cpu_count())
 
     # ---- quant
