@@ -146,7 +146,7 @@ def workload_config(tokens, gpus):
             "tokens": tokens, "hidden": H, "intermediate": I, "experts": E, "top_k": TOPK, "routing": "softmax top-4 renormalised",
             "weights": "E2M1 codes uniform, E8M0 scales 2^-7..2^-3, seed 0", "activations": "bf16 N(0,1), logits fp32 N(0,1)",
             "parallelism": "single GPU" if gpus == 1 else f"expert parallel ep{gpus}, {E // gpus} experts per GPU",
-            "l2": L2_NOTE + "; 8 rotating inputs",
+            "l2": L2_NOTE + ("; 8 rotating inputs" if gpus == 1 else "; 4 rotating inputs per rank"),
             "timing": "CUDA-graph replay of the whole-layer C-ABI call, CUDA events per step"}
 
 
