@@ -25,7 +25,7 @@
 namespace b200moe {
 
 // ------------------------------------------------------------------------------------------------ kernel
-template <int MODE, int BM>
+template <int MODE, int BM, bool DUAL = false>
 struct Cfg {
   static constexpr int kTilesM = MODE == 1 ? kW13Tiles : kW2Tiles;
   static constexpr int kTilesK = MODE == 1 ? kK1Tiles : kK2Tiles;
@@ -39,12 +39,14 @@ struct Cfg {
   // bm = 128 (prefill): the token block is the 128-row M operand and the weight tile is N, so a TMEM lane is a token and
   // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
   static constexpr bool kTokensAreM = BM == 128;
-  // GEMM1 at bm = 128 is bound by what its issuing threads can issue, so it runs TWO CTAs per SM, each with half the
-  // pipeline (3 stages), one accumulator buffer and one epilogue group: two independent instruction streams feed the
-  // tensor pipe, and one CTA's epilogue overlaps the other's MMAs.
-  static constexpr int kCtasPerSm = (MODE == 1 && BM == 128) ? 2 : 1;
+  // DUAL (GEMM1 at bm = 128, many rows): the kernel is then bound by what its issuing threads can issue, so it runs TWO
+  // CTAs per SM, each with half the pipeline (3 stages), one accumulator buffer and one epilogue group: two independent
+  // instruction streams feed the tensor pipe, and one CTA's epilogue overlaps the other's MMAs. With fewer rows the
+  // kernel is bound by the weight read and the single CTA with its deeper pipeline is a little faster.
+  static_assert(!DUAL || (MODE == 1 && BM == 128), "two CTAs per SM: GEMM1 at 128-row blocks only");
+  static constexpr int kCtasPerSm = DUAL ? 2 : 1;
   static constexpr int kAccBufs = kCtasPerSm == 2 ? 1 : 2;
-  static constexpr int kStages = BM == 128 ? (MODE == 1 ? 3 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
+  static constexpr int kStages = BM == 128 ? (MODE == 1 ? (DUAL ? 3 : 6) : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
   // bm = 128 GEMM2 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
   static constexpr int kEpiGroups = (kTokensAreM && kAccBufs == 2) ? 2 : 1;
   // warps: 0 = copy producer, 1 = MMA issue, 2 .. = epilogue groups, last = scale-copy issue
@@ -142,13 +144,13 @@ __device__ __forceinline__ RowPlacer make_placer(const EpilogueArgs& ep, __nv_bf
   return p;
 }
 
-template <int MODE, int BM>
-__global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), (Cfg<MODE, BM>::kCtasPerSm))
+template <int MODE, int BM, bool DUAL = false>
+__global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM, DUAL>::kCtasPerSm))
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                         const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
                         const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status, int num_experts,
                         int max_blocks) {
-  using C = Cfg<MODE, BM>;
+  using C = Cfg<MODE, BM, DUAL>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
@@ -948,18 +950,19 @@ __global__ void __launch_bounds__(256, 1)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-template <int MODE, int BM>
+constexpr int64_t kDualFromRows = 36000;  // upper bound of sorted rows from which GEMM1 runs two CTAs per SM
+template <int MODE, int BM, bool DUAL = false>
 static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
                   int num_experts, int32_t* status, cudaStream_t stream) {
-  using C = Cfg<MODE, BM>;
+  using C = Cfg<MODE, BM, DUAL>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (C::kCtasPerSm > 1) {  // two CTAs need the whole shared-memory carve-out of the SM
-      e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributePreferredSharedMemoryCarveout,
+      e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM, DUAL>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
       if (e != cudaSuccess) return static_cast<int>(e);
     }
@@ -969,7 +972,7 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
   const int64_t ctas = static_cast<int64_t>(sm_count()) * C::kCtasPerSm;
   const int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
   if (grid <= 0) return 0;
-  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
+  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM, DUAL>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
 
@@ -981,7 +984,12 @@ static int launch_bm(int bm, const CUtensorMap& mx, const uint8_t* w_tiles, cons
     case 16: return launch<MODE, 16>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
     case 32: return launch<MODE, 32>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
     case 64: return launch<MODE, 64>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
-    case 128: return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
+    case 128:
+      // two CTAs per SM from ~5000 tokens' worth of sorted rows on (measured: 8192 tokens 210 -> 190 us, 2048 tokens
+      // 126 -> 129 us)
+      if (MODE == 1 && max_rows >= kDualFromRows)
+        return launch<1, 128, true>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
+      return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
   }
   return B200MOE_E_ARG;
 }

@@ -488,7 +488,7 @@ def _with_shared(x, w, logits, shared, return_partials):
     return (slots, shared) if return_partials else reduce_slots(slots, shared)
 
 
-WARM_UP_TOKENS = (1, 64, 481, 1025, 1729)  # one-launch GEMMs, then one size per block height (16, 32, 64, 128)
+WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000)  # one-launch GEMMs, one size per block height, the two-CTA GEMM1
 
 
 def warm_up_mxfp4_moe(w, *, partials=False, workers=None):
