@@ -4,20 +4,20 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
 E_ARG, E_ALIGN, E_DRIVER, E_TOO_LARGE = -1, -2, -3, -4
-DEV_TIMEOUT = 1
+DEV_TIMEOUT, DEV_BAD_INDEX = 1, 2
 ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
 
 
 class Weights(Structure):
     """struct b200moe_weights"""
     _fields_ = [("w13t", c_void_p), ("w2t", c_void_p), ("bias", c_void_p),
-                ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float)]
+                ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float), ("gate", c_void_p)]
 
 
 _P = c_void_p
@@ -61,6 +61,12 @@ SIGNATURES = {
     "b200moe_sidecar_unpack": (c_int, [_P, _P, _P, _P, c_int64, _P, _P]),
     "b200moe_router_gemm_quant": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
     "b200moe_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "b200moe_workspace_bytes_x": (c_size_t, [c_int64, c_int]),
+    "b200moe_forward_x": (c_int, [POINTER(Weights), _P, c_int64, _P, c_size_t, _P, _P, _P, _P]),
+    "b200moe_set_wait_limit_ns": (c_int, [c_uint64]),
+    "b200moe_route_sort_partials": (c_int, [_P, c_int64, c_int64, c_int, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P,
+                                            _P, _P, _P, _P, _P, _P]),
+    "b200moe_reduce_slots_add_rmsnorm_quant": (c_int, [_P, _P, _P, _P, c_float, c_int64, _P, _P, _P, _P, _P]),
     "b200moe_forward": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, c_size_t, _P, _P, _P, _P]),
     "b200moe_forward_host": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, _P, _P, c_size_t, _P, _P, _P, _P, _P]),
 }

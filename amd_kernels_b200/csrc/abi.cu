@@ -18,12 +18,22 @@ struct Workspace {
   uint8_t* hq;            // [R][384]
   uint8_t* sfh;           // [R/bm][6][512]
   int32_t* done;          // [R/bm] GEMM1 tiles finished per row block (one-launch GEMM1+GEMM2)
+  // only with the router inside the call (b200moe_forward_x):
+  float* partials;        // [S][T][E] split-K logit partials
+  uint8_t* q4;            // [T][3072] row-major MXFP4 codes of x
+  uint8_t* s4;            // [T][192] their scales
   size_t bytes;
   int bm;
   int64_t rows;
 };
 
-static Workspace carve(uint8_t* base, int64_t tokens, int num_experts) {
+int dispatch_rows_done(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids, const int32_t* num_valid,
+                       int64_t tokens, int bm, int by_pair, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
+                       int32_t* done, void* stream);
+int set_wait_limit_routed(unsigned long long ns);
+int set_wait_limit_shared(unsigned long long ns);
+
+static Workspace carve(uint8_t* base, int64_t tokens, int num_experts, bool with_router = false) {
   Workspace ws{};
   ws.bm = b200moe_block_rows(tokens);
   ws.rows = b200moe_max_sorted_rows(tokens, ws.bm, num_experts);
@@ -46,6 +56,11 @@ static Workspace carve(uint8_t* base, int64_t tokens, int num_experts) {
   ws.hq = take(ws.rows * (kI / 2));
   ws.sfh = take(blocks * (kI / 128) * kAtomBytes);
   ws.done = reinterpret_cast<int32_t*>(take(blocks * 4));
+  if (with_router) {
+    ws.partials = reinterpret_cast<float*>(take(static_cast<size_t>(b200moe_router_splits(tokens)) * tokens * num_experts * 4));
+    ws.q4 = take(tokens * (kH / 2));
+    ws.s4 = take(tokens * (kH / 32));
+  }
   ws.bytes = off;
   return ws;
 }
@@ -58,6 +73,67 @@ extern "C" const char* b200moe_arch(void) { return "sm_100a"; }
 extern "C" size_t b200moe_workspace_bytes(int64_t tokens, int num_experts) {
   if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 1 || num_experts > b200moe::kMaxE) return 0;
   return b200moe::carve(nullptr, tokens, num_experts).bytes;
+}
+
+extern "C" size_t b200moe_workspace_bytes_x(int64_t tokens, int num_experts) {
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 1 || num_experts > b200moe::kMaxE) return 0;
+  return b200moe::carve(nullptr, tokens, num_experts, true).bytes;
+}
+
+extern "C" int b200moe_set_wait_limit_ns(uint64_t ns) {
+  if (ns == 0) return B200MOE_E_ARG;
+  int r = b200moe::set_wait_limit_routed(ns);
+  if (r) return r;
+  return b200moe::set_wait_limit_shared(ns);
+}
+
+namespace b200moe {
+// sorted, gathered, quantised rows are in the workspace: the grouped GEMMs and the reduce
+static int experts_and_reduce(const b200moe_weights* w, const Workspace& ws, int64_t tokens, void* slots_bf16,
+                              void* out_bf16, int32_t* status, void* stream) {
+  const int ne = w->num_experts;
+  int r;
+  if (tokens <= 32) {  // small batches: both grouped GEMMs in one persistent launch (measured faster there only)
+    if ((r = b200moe_gemm12(w->w13t, w->w2t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.sorted_ids,
+                            ws.sorted_w, ws.rows, ws.bm, tokens, ws.hq, ws.sfh, ws.done, slots_bf16, status, stream)))
+      return r;
+  } else {
+    if ((r = b200moe_gemm1_swiglu_quant(w->w13t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows, ws.bm,
+                                        ws.hq, ws.sfh, w->w2t, status, stream)))
+      return r;
+    if ((r = b200moe_gemm2_weighted(w->w2t, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids, ws.sorted_w,
+                                    ws.rows, ws.bm, tokens, slots_bf16, status, stream)))
+      return r;
+  }
+  if (out_bf16 && (r = b200moe_reduce_slots(slots_bf16, nullptr, tokens, out_bf16, stream))) return r;
+  return 0;
+}
+}  // namespace b200moe
+
+extern "C" int b200moe_forward_x(const b200moe_weights* w, const void* x_bf16, int64_t tokens, void* workspace,
+                                 size_t workspace_bytes, void* slots_bf16, void* out_bf16, int32_t* status,
+                                 void* stream) {
+  using namespace b200moe;
+  if (!w || !x_bf16 || !workspace || !slots_bf16 || !status || !w->gate) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > B200MOE_MAX_TOKENS) return B200MOE_E_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return B200MOE_E_ALIGN;
+  const int ne = w->num_experts;
+  Workspace ws = carve(static_cast<uint8_t*>(workspace), tokens, ne, true);
+  if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
+  const int splits = b200moe_router_splits(tokens);
+  int r;
+  // one pass over x: logit partials and the MXFP4 operands, row-major
+  if ((r = b200moe_router_gemm_quant(x_bf16, w->gate, tokens, ne, splits, ws.partials, ws.q4, ws.s4, nullptr, nullptr,
+                                     stream)))
+    return r;
+  if ((r = b200moe_route_sort_partials(ws.partials, ne, tokens * ne, splits, w->bias, tokens, ne, w->route_mode,
+                                       w->route_scale, ws.bm, ws.w, ws.ids, ws.sorted_ids, ws.sorted_w, ws.block_expert,
+                                       ws.num_valid, ws.scratch, stream)))
+    return r;
+  if ((r = dispatch_rows_done(ws.q4, ws.s4, ws.sorted_ids, ws.num_valid, tokens, ws.bm, 0, ws.rows, ws.xq_sorted, ws.sfx,
+                              ws.done, stream)))
+    return r;
+  return experts_and_reduce(w, ws, tokens, slots_bf16, out_bf16, status, stream);
 }
 
 extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, const float* logits, int64_t tokens,
@@ -77,21 +153,7 @@ extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, con
   if ((r = b200moe_quant_dispatch(x_bf16, ws.sorted_ids, ws.num_valid, tokens, ws.bm, ws.rows, ws.xq_sorted, ws.sfx,
                                   ws.done, stream)))
     return r;
-  if (tokens <= 32) {  // small batches: both grouped GEMMs in one persistent launch (measured faster there only)
-    if ((r = b200moe_gemm12(w->w13t, w->w2t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.sorted_ids,
-                            ws.sorted_w, ws.rows, ws.bm, tokens, ws.hq, ws.sfh, ws.done, slots_bf16, status, stream)))
-      return r;
-    if (out_bf16 && (r = b200moe_reduce_slots(slots_bf16, nullptr, tokens, out_bf16, stream))) return r;
-    return 0;
-  }
-  if ((r = b200moe_gemm1_swiglu_quant(w->w13t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.rows, ws.bm,
-                                      ws.hq, ws.sfh, w->w2t, status, stream)))
-    return r;
-  if ((r = b200moe_gemm2_weighted(w->w2t, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids, ws.sorted_w,
-                                  ws.rows, ws.bm, tokens, slots_bf16, status, stream)))
-    return r;
-  if (out_bf16 && (r = b200moe_reduce_slots(slots_bf16, nullptr, tokens, out_bf16, stream))) return r;
-  return 0;
+  return experts_and_reduce(w, ws, tokens, slots_bf16, out_bf16, status, stream);
 }
 
 extern "C" int b200moe_forward_host(const b200moe_weights* w, const void* host_x_bf16, const float* host_logits,

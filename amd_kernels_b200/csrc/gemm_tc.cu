@@ -157,6 +157,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
   __shared__ __align__(8) uint64_t bar_sf[C::kStages];  // the stage's scales are in tensor memory
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_drain[2];  // used after an abort only
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ __nv_bfloat16* s_dst[MODE == 2 ? BM : 1];
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
       mbar_init(smem_u32(&bar_tempty[a]), 128);
+      mbar_init(smem_u32(&bar_drain[a]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -262,12 +264,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
       }
       if (!ok) {
         // aborting: let the copies already in flight land before the CTA gives up its shared memory
-        const uint32_t pending = it < C::kStages ? it : C::kStages;
-        for (uint32_t j = 0; j < pending; ++j) {
-          const uint32_t idx = it - 1 - j, s = idx % C::kStages, ph = (idx / C::kStages) & 1u;
-          const uint64_t t0 = global_timer();
-          while (!mbar_try_wait(smem_u32(&bar_full[s]), ph) && global_timer() - t0 < kWaitLimitNs) {}
-        }
+        drain_copies(bar_full, it, C::kStages);
       }
     }
   } else if (warp == 1) {
@@ -315,6 +312,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
     }
   } else if (warp == C::kScaleWarp) {
     // ---------------------------------------------------------------- scale copies: shared memory -> tensor memory
@@ -343,6 +341,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
           }
         }
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
     }
   } else {
     // ---------------------------------------------------------------- epilogue (groups of 4 warps, TMEM lane quarter = warp % 4)
@@ -591,7 +590,7 @@ __device__ __forceinline__ bool wait_count(const int32_t* counter, int target, v
     if (v >= target) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer() - t0 > kWaitLimitNs) {
+      if (global_timer() - t0 > wait_limit_ns()) {
         *abort_flag = 1;
         atomicExch(status, B200MOE_DEV_TIMEOUT);
         return false;
@@ -615,6 +614,7 @@ __global__ void __launch_bounds__(256, 1)
   __shared__ __align__(8) uint64_t bar_sf[CC::kStages];  // the stage's scales are in tensor memory (warp 7 copies them)
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_drain[2];  // used after an abort only
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ __nv_bfloat16* s_dst[BM];
@@ -635,6 +635,7 @@ __global__ void __launch_bounds__(256, 1)
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
       mbar_init(smem_u32(&bar_tempty[a]), 128);
+      mbar_init(smem_u32(&bar_drain[a]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -700,12 +701,7 @@ __global__ void __launch_bounds__(256, 1)
         }
       }
       if (!ok) {
-        const uint32_t pending = it < CC::kStages ? it : CC::kStages;
-        for (uint32_t j = 0; j < pending; ++j) {
-          const uint32_t idx = it - 1 - j, s = idx % CC::kStages, ph = (idx / CC::kStages) & 1u;
-          const uint64_t t0 = global_timer();
-          while (!mbar_try_wait(smem_u32(&bar_full[s]), ph) && global_timer() - t0 < kWaitLimitNs) {}
-        }
+        drain_copies(bar_full, it, CC::kStages);
       }
     }
   } else if (warp == 6) {
@@ -726,9 +722,9 @@ __global__ void __launch_bounds__(256, 1)
         if (second) {
           // h of this row block must be complete and visible to the copy engine before it is read. The count was
           // fetched while the previous unit's copies were issued, so the usual case costs no memory round trip.
-          // Usual case: the count is already 12. The writers ordered their stores for the copy engine before they
-          // counted (see the GEMM1 epilogue) and the copy below cannot issue before this branch has seen the count,
-          // so no fence is needed here; fences in this thread would wait for its own copies in flight.
+          // Usual case: the look-ahead (an acquire load: a load, not a fence, so it does not wait for this thread's
+          // copies in flight) has already seen 12. The writers ordered their stores for the copy engine before they
+          // counted (see the GEMM1 epilogue), so no fence is needed here.
           if (!(have_next && next_count >= kW13Tiles)) {
             if (!wait_count(done + b, kW13Tiles, abort_v, status)) { ok = false; break; }
             asm volatile("fence.proxy.async;" ::: "memory");
@@ -745,7 +741,7 @@ __global__ void __launch_bounds__(256, 1)
         const int un = u + static_cast<int>(gridDim.x);  // look ahead: the next unit's completion count
         have_next = un < total_units && un >= units1;
         if (have_next)
-          asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(next_count) : "l"(done + (un - units1) / kW2Tiles) : "memory");
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(next_count) : "l"(done + (un - units1) / kW2Tiles) : "memory");
       }
     }
   } else if (warp == 1) {
@@ -783,6 +779,7 @@ __global__ void __launch_bounds__(256, 1)
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
     }
   } else if (warp == 7) {
     // ---------------------------------------------------------------- scale copies: shared memory -> tensor memory
@@ -810,6 +807,7 @@ __global__ void __launch_bounds__(256, 1)
           }
         }
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
     }
   } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
@@ -956,8 +954,8 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
                   int num_experts, int32_t* status, cudaStream_t stream) {
   using C = Cfg<MODE, BM, DUAL>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce once;
+  const int rc = once.run([] {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -966,8 +964,9 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
                                cudaSharedmemCarveoutMaxShared);
       if (e != cudaSuccess) return static_cast<int>(e);
     }
-    configured = true;
-  }
+    return 0;
+  });
+  if (rc) return rc;
   const int64_t max_units = max_rows / BM * C::kTilesM;
   const int64_t ctas = static_cast<int64_t>(sm_count()) * C::kCtasPerSm;
   const int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
@@ -1000,12 +999,11 @@ static int launch12(const CUtensorMap& mx, const CUtensorMap& mh, const uint8_t*
                     const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep,
                     int32_t* done, int64_t max_rows, int num_experts, int32_t* status, cudaStream_t stream) {
   using CC = Cfg12<BM>;
-  static bool configured = false;
-  if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm12_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, CC::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int rc = once.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(gemm12_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, CC::kSmemBytes));
+  });
+  if (rc) return rc;
   const int64_t max_units = max_rows / BM * (kW13Tiles + kW2Tiles);
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   if (grid <= 0) return 0;
@@ -1013,6 +1011,8 @@ static int launch12(const CUtensorMap& mx, const CUtensorMap& mh, const uint8_t*
                  done, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
+
+int set_wait_limit_routed(unsigned long long ns) { return set_wait_limit_here(ns); }
 
 }  // namespace b200moe
 

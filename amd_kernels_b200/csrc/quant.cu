@@ -34,30 +34,39 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const uint4* __restric
 }
 
 // One warp per sorted row: copies the token's 3072 code bytes and scatters its 192 scale bytes into the block's atoms.
+// Also zeroes `done` (may be null), the per-block completion counts of a following one-launch GEMM1+GEMM2.
 __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __restrict__ codes,
                                                             const uint8_t* __restrict__ scales,
                                                             const int32_t* __restrict__ sorted_ids,
                                                             const int32_t* __restrict__ num_valid, int64_t tokens,
                                                             int bm, int by_pair, uint8_t* __restrict__ xq_sorted,
-                                                            uint8_t* __restrict__ sfx) {
+                                                            uint8_t* __restrict__ sfx, int32_t* __restrict__ done,
+                                                            int n_done) {
+  pdl_enter(codes, scales, sorted_ids, num_valid);
+  {
+    const int64_t z = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (done != nullptr && z < n_done) done[z] = 0;
+  }
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= num_valid[0]) return;
-  const int sid = sorted_ids[row];
+  if (row >= __ldcg(num_valid)) return;
+  const int sid = __ldcg(sorted_ids + row);
   const bool pad = (sid & 0x00ffffff) >= tokens;
   // source row: the token, or (by_pair) the pair 4*token+slot when every (token, slot) carries its own quantised row
   const int64_t token = by_pair ? static_cast<int64_t>(sid & 0x00ffffff) * kTopK + (sid >> 24) : (sid & 0x00ffffff);
   uint4* dst = reinterpret_cast<uint4*>(xq_sorted + row * (kH / 2));
   const uint4* src = reinterpret_cast<const uint4*>(codes + token * (kH / 2));
+  uint4 v[(kH / 2) / 16 / 32];
 #pragma unroll
-  for (int j = 0; j < (kH / 2) / 16 / 32; ++j)
-    dst[j * 32 + lane] = pad ? make_uint4(0, 0, 0, 0) : src[j * 32 + lane];
+  for (int j = 0; j < (kH / 2) / 16 / 32; ++j) v[j] = pad ? make_uint4(0, 0, 0, 0) : __ldcg(src + j * 32 + lane);
+#pragma unroll
+  for (int j = 0; j < (kH / 2) / 16 / 32; ++j) dst[j * 32 + lane] = v[j];
   const int64_t block = row / bm;
   const int r = static_cast<int>(row % bm);
   const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(scales + token * (kH / 32));
   uint8_t* sdst = sfx + block * (kH / 128) * kAtomBytes + atom_offset(r, 0);
-  for (int a = lane; a < kH / 128; a += 32)
-    *reinterpret_cast<uint32_t*>(sdst + a * kAtomBytes) = pad ? 0x7f7f7f7fu : ssrc[a];
+  for (int a = lane; a < kH / 128; a += 32)  // a padding row: zero codes, the scale byte of an all-zero block
+    *reinterpret_cast<uint32_t*>(sdst + a * kAtomBytes) = pad ? 0x01010101u : __ldcg(ssrc + a);
 }
 
 // Quantisation fused with the gather: one 256-thread CTA per sorted row reads the token's bf16 row (three 16-byte loads
@@ -252,10 +261,10 @@ extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, ui
   return 0;
 }
 
-extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
-                                     const int32_t* num_valid, int64_t tokens, int bm, int by_pair, int64_t max_rows,
-                                     uint8_t* xq_sorted, uint8_t* sfx, void* stream) {
-  using namespace b200moe;
+namespace b200moe {
+int dispatch_rows_done(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids, const int32_t* num_valid,
+                       int64_t tokens, int bm, int by_pair, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
+                       int32_t* done, void* stream) {
   if (!codes || !scales || !sorted_ids || !num_valid || !xq_sorted || !sfx || tokens < 0 || max_rows < 0)
     return B200MOE_E_ARG;
   if (bm != 16 && bm != 32 && bm != 64 && bm != 128) return B200MOE_E_ARG;
@@ -264,8 +273,17 @@ extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
   const unsigned grid = static_cast<unsigned>((max_rows + 7) / 8);
-  B200MOE_LAUNCH_PLAIN(dispatch_rows_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), codes, scales, sorted_ids, num_valid, tokens, bm, by_pair, xq_sorted, sfx);
+  B200MOE_LAUNCH(dispatch_rows_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), codes, scales, sorted_ids,
+                 num_valid, tokens, bm, by_pair, xq_sorted, sfx, done, static_cast<int>(max_rows / bm));
   return 0;
+}
+}  // namespace b200moe
+
+extern "C" int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
+                                     const int32_t* num_valid, int64_t tokens, int bm, int by_pair, int64_t max_rows,
+                                     uint8_t* xq_sorted, uint8_t* sfx, void* stream) {
+  return b200moe::dispatch_rows_done(codes, scales, sorted_ids, num_valid, tokens, bm, by_pair, max_rows, xq_sorted, sfx,
+                                     nullptr, stream);
 }
 
 extern "C" int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid,

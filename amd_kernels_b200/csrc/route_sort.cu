@@ -1,6 +1,6 @@
 // Router top-4 and the routing sort (a stable counting sort of the 4T (token, slot) pairs by expert with per-expert
-// padding to bm rows). For T <= 256 both run in ONE single-CTA kernel; above that the router is its own grid and the
-// sort runs as a count pass and a placement pass over 1024-pair chunks.
+// padding to bm rows). Up to 32 tokens both run in ONE single-CTA kernel; above that the router is its own grid and the
+// sort runs as a count pass (above 256 tokens) and a placement pass over 1024-pair chunks.
 //
 // Determinism: counts are order-free; placement ranks come from warp match/popc and fixed-order prefix sums, so the row
 // order inside an expert is the pair order 4*token+slot on every run.
@@ -238,9 +238,11 @@ __global__ void __launch_bounds__(kChunk) permute_place_kernel(const int32_t* __
   place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, cta_counts, sorted_ids, sorted_w, block_expert, num_valid);
 }
 
-// T <= 256: routing and the sort in one CTA. Warp w routes tokens w, w+32, ...
+// Up to 32 tokens: routing and the sort in one CTA. Warp w routes tokens w, w+32, ... `logits` are plain logits
+// (splits = 1) or split-K partials added in split order (row t at t*stride_t, split s at s*stride_s).
 template <int MODE>
-__global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restrict__ logits,
+__global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restrict__ logits, int64_t stride_t,
+                                                            int64_t stride_s, int splits,
                                                             const float* __restrict__ bias, int tokens,
                                                             int num_experts, float scale, int bm_shift,
                                                             float* __restrict__ out_w, int32_t* __restrict__ out_ids,
@@ -256,7 +258,7 @@ __global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restr
   for (int t = warp; t < tokens; t += 32) {
     float w[4];
     int id[4];
-    route_token<MODE>(logits + static_cast<int64_t>(t) * num_experts, 0, 1, bias, num_experts, scale, lane, w, id);
+    route_token<MODE>(logits + static_cast<int64_t>(t) * stride_t, stride_s, splits, bias, num_experts, scale, lane, w, id);
     if (lane < 4) {
       float wv = w[0];
       int iv = id[0];
@@ -339,30 +341,42 @@ extern "C" int b200moe_permute(const int32_t* ids, const float* w, int64_t token
   return 0;
 }
 
-extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, int num_experts, int mode,
-                                  float scale, int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids,
-                                  float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch,
-                                  void* stream) {
+extern "C" int b200moe_route_sort_partials(const float* partials, int64_t stride_t, int64_t stride_s, int splits,
+                                           const float* bias, int64_t tokens, int num_experts, int mode, float scale,
+                                           int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids, float* sorted_w,
+                                           int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream) {
   using namespace b200moe;
-  if (!logits || !out_w || !out_ids || !sorted_ids || !sorted_w || !block_expert || !num_valid) return B200MOE_E_ARG;
+  if (!partials || !out_w || !out_ids || !sorted_ids || !sorted_w || !block_expert || !num_valid || splits < 1)
+    return B200MOE_E_ARG;
   if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 4 || num_experts > kMaxE) return B200MOE_E_ARG;
   if (mode != B200MOE_ROUTE_SIGMOID_BIAS && mode != B200MOE_ROUTE_SOFTMAX) return B200MOE_E_ARG;
   const int shift = shift_of(bm);
   if (shift < 0) return B200MOE_E_ARG;
   if (tokens > kFusedRouteTokens) {  // many tokens: route on many SMs first, then sort
-    int r = b200moe_route_topk(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, out_w, out_ids, stream);
+    int r = b200moe_route_topk(partials, stride_t, stride_s, splits, bias, tokens, num_experts, mode, scale, out_w,
+                               out_ids, stream);
     if (r) return r;
     return b200moe_permute(out_ids, out_w, tokens, num_experts, bm, sorted_ids, sorted_w, block_expert, num_valid, scratch,
                            stream);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (mode == B200MOE_ROUTE_SIGMOID_BIAS)
-    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SIGMOID_BIAS>), 1, kChunk, 0, s, logits, bias, static_cast<int>(tokens),
-                   num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, num_valid);
+    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SIGMOID_BIAS>), 1, kChunk, 0, s, partials, stride_t, stride_s, splits,
+                   bias, static_cast<int>(tokens), num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w,
+                   block_expert, num_valid);
   else
-    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SOFTMAX>), 1, kChunk, 0, s, logits, bias, static_cast<int>(tokens),
-                   num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, num_valid);
+    B200MOE_LAUNCH((route_sort_kernel<B200MOE_ROUTE_SOFTMAX>), 1, kChunk, 0, s, partials, stride_t, stride_s, splits, bias,
+                   static_cast<int>(tokens), num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert,
+                   num_valid);
   return 0;
+}
+
+extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, int num_experts, int mode,
+                                  float scale, int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids,
+                                  float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch,
+                                  void* stream) {
+  return b200moe_route_sort_partials(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, bm, out_w, out_ids,
+                                     sorted_ids, sorted_w, block_expert, num_valid, scratch, stream);
 }
 
 // ------------------------------------------------------------------------------------------------ allocation-free sort

@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(224, 1)
   __shared__ __align__(8) uint64_t bar_sf[C::kStages];
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_drain[2];  // used after an abort only
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(224, 1)
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
       mbar_init(smem_u32(&bar_tempty[a]), 128);
+      mbar_init(smem_u32(&bar_drain[a]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -188,12 +190,7 @@ __global__ void __launch_bounds__(224, 1)
         }
       }
       if (!ok) {
-        const uint32_t pending = it < C::kStages ? it : C::kStages;
-        for (uint32_t j = 0; j < pending; ++j) {
-          const uint32_t idx = it - 1 - j, s = idx % C::kStages, ph = (idx / C::kStages) & 1u;
-          const uint64_t t0 = global_timer();
-          while (!mbar_try_wait(smem_u32(&bar_full[s]), ph) && global_timer() - t0 < kWaitLimitNs) {}
-        }
+        drain_copies(bar_full, it, C::kStages);
       }
     }
   } else if (warp == 1) {
@@ -229,6 +226,7 @@ __global__ void __launch_bounds__(224, 1)
         }
         if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
     }
   } else if (warp == 6) {
     if (lane == 0) {  // ------------------------------------------------ scale copies: shared memory -> tensor memory
@@ -252,6 +250,7 @@ __global__ void __launch_bounds__(224, 1)
           }
         }
       }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -347,13 +346,12 @@ template <int MODE, int BM>
 static int launch_shared(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x, int n_blocks,
                          const SharedEpilogue& ep, int32_t* status, cudaStream_t stream) {
   using C = Cfg8<MODE, BM>;
-  static bool configured = false;
-  if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(shared_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               C::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int rc = once.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(shared_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 C::kSmemBytes));
+  });
+  if (rc) return rc;
   const int units = n_blocks * C::kTilesM;
   const int grid = units < sm_count() ? units : sm_count();
   if (grid <= 0) return 0;
@@ -400,6 +398,8 @@ static SharedWorkspace carve_shared(uint8_t* base, int64_t tokens) {
   ws.bytes = off;
   return ws;
 }
+
+int set_wait_limit_shared(unsigned long long ns) { return set_wait_limit_here(ns); }
 
 }  // namespace b200moe
 

@@ -3,6 +3,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "../../include/b200_moe.h"
 
 namespace b200moe {
@@ -37,15 +39,40 @@ static inline int make_map(CUtensorMap* map, const void* base, uint64_t row_byte
   return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
 }
 
+constexpr int kMaxDevices = 64;
+
+// SM count of the CURRENT device, looked up once per device (a process may drive several GPUs through this library).
 static inline int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
+  static std::mutex mu;
+  static int counts[kMaxDevices] = {};
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (counts[dev] == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    counts[dev] = v;
+  }
+  return counts[dev];
 }
+
+// Function attributes (dynamic shared-memory size, carve-out) belong to a device: `configure` runs once per device and
+// kernel instantiation, with that device current, under a lock. One instance per launch-site template instantiation.
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+  template <typename F>
+  int run(F&& configure) {
+    int dev = 0;
+    const cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return B200MOE_E_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev]) return 0;
+    const int r = configure();
+    if (r == 0) done[dev] = true;
+    return r;
+  }
+};
 
 
 static inline bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }

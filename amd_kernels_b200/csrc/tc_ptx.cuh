@@ -34,7 +34,16 @@ __device__ __forceinline__ uint64_t global_timer() {
   return t;
 }
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// How long a device-side wait may last before the kernel gives up (status B200MOE_DEV_TIMEOUT). Every translation
+// unit that includes this header carries its own copy; b200moe_set_wait_limit_ns updates all of them on the current
+// device. Read only on the slow path of a wait.
+static __device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+__device__ __forceinline__ uint64_t wait_limit_ns() {
+  return *reinterpret_cast<volatile unsigned long long*>(&g_wait_limit_ns);
+}
+static inline int set_wait_limit_here(unsigned long long ns) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns)));
+}
 
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
@@ -45,12 +54,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer() - t0 > kWaitLimitNs) {
+      if (global_timer() - t0 > wait_limit_ns()) {
         *abort_flag = 1;
         atomicExch(status, B200MOE_DEV_TIMEOUT);
         return false;
       }
     }
+  }
+}
+
+// After an abort: let the copies of the last `stages` pipeline slots land (one overall limit, not one per slot) before
+// the CTA gives up its shared memory. `it` = stages issued so far.
+__device__ __forceinline__ void drain_copies(const uint64_t* bar_full, uint32_t it, uint32_t stages) {
+  const uint32_t pending = it < stages ? it : stages;
+  const uint64_t t0 = global_timer(), limit = wait_limit_ns();
+  for (uint32_t j = 0; j < pending; ++j) {
+    const uint32_t idx = it - 1 - j, s = idx % stages, ph = (idx / stages) & 1u;
+    while (!mbar_try_wait(static_cast<uint32_t>(__cvta_generic_to_shared(bar_full + s)), ph) && global_timer() - t0 < limit) {}
   }
 }
 
@@ -69,6 +89,13 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// After an abort: wait (bounded) until every tcgen05 operation this thread issued has completed, so tensor memory is
+// not freed under an MMA or a scale copy still in flight. `bar` is a barrier nothing else uses (count 1, phase 0).
+__device__ __forceinline__ void drain_tcgen05(uint32_t bar) {
+  tc_commit(bar);
+  const uint64_t t0 = global_timer(), limit = wait_limit_ns();
+  while (!mbar_try_wait(bar, 0) && global_timer() - t0 < limit) {}
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(

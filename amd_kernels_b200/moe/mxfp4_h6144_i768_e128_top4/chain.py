@@ -101,6 +101,10 @@ class MoeWeights:
             _lib.check(lib.b200moe_preshuffle_w2(_ptr(w2), _ptr(w2_scale), n_exp, _ptr(w2t), _stream(dev)),
                        "preshuffle_w2")
         bias = None if correction_bias is None else correction_bias.to(device=dev, dtype=torch.float32).contiguous()
+        if router_weight is not None:
+            if tuple(router_weight.shape) != (n_exp, H):
+                raise ValueError(f"router_weight: needs ({n_exp}, {H}), got {tuple(router_weight.shape)}")
+            router_weight = router_weight.to(device=dev, dtype=torch.float32).contiguous()
         return cls(router_weight, bias, w13t, None, w2t, None, float(routed_scaling_factor), routing_mode,
                    shared_weights=shared, row_major=(w13, w13_scale, w2, w2_scale) if keep_row_major else None)
 
@@ -111,10 +115,14 @@ class MoeWeights:
     def abi(self) -> _lib.Weights:
         """``struct b200moe_weights`` over this object's tensors."""
         if self._abi is None:
+            gate = self.router_weight
+            if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.device != self.w13.device
+                                     or tuple(gate.shape) != (self.num_experts, H)):
+                raise ValueError(f"router_weight: expected contiguous fp32 [{self.num_experts}, {H}] on {self.w13.device}")
             self._abi = _lib.Weights(self.w13.data_ptr(), self.w2.data_ptr(),
                                      None if self.correction_bias is None else self.correction_bias.data_ptr(),
                                      self.num_experts, ROUTING_MODES[self.routing_mode],
-                                     self.routed_scaling_factor)
+                                     self.routed_scaling_factor, None if gate is None else gate.data_ptr())
         return self._abi
 
 
@@ -265,13 +273,15 @@ def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_nex
     return hq, sfh
 
 
-def grouped_gemm12(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, slots=None):
+def grouped_gemm12(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, slots=None, done=None):
     """Both grouped GEMMs in one persistent launch (block heights 16 / 32 / 64): -> (slots, h codes, h scale atoms), the
-    same bits as ``grouped_gemm1`` followed by ``grouped_gemm2`` (reference gemm12_a4w4.py:24)."""
+    same bits as ``grouped_gemm1`` followed by ``grouped_gemm2`` (reference gemm12_a4w4.py:24). ``done``: the per-block
+    completion counts, int32 [rows / bm], zero on entry (allocated when not given)."""
     dev = xq_sorted.device
     hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
-    done = torch.zeros(sort.max_rows // sort.bm, dtype=torch.int32, device=dev)
+    if done is None:
+        done = torch.zeros(sort.max_rows // sort.bm, dtype=torch.int32, device=dev)
     if slots is None:
         slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
     _lib.check(_lib.load().b200moe_gemm12(_ptr(w.w13), _ptr(w.w2), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
@@ -431,7 +441,8 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     returns (slots BF16 [M, 4, H], shared BF16 [M, H]); without ``w.shared_weights`` the shared term is absent (None).
     ``router_logits`` fp32 [M, E] skips the router GEMM. The routed part is one ``b200moe_forward`` on the current
     stream; the shared expert runs on the device's side stream beside it and the current stream joins it before the
-    reduce. Scratch and outputs come from ``torch.empty``."""
+    reduce. Without ``router_logits`` the router runs inside the same call (``b200moe_forward_x``). Scratch and outputs come
+    from ``torch.empty``."""
     if not isinstance(x, torch.Tensor):
         from .prepared_input import MoeInput, MoeInputCompact, mxfp4_moe_prepared
         if not isinstance(x, (MoeInput, MoeInputCompact)):
@@ -440,7 +451,6 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
     variant_for(x.shape[0])
     if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("expected contiguous BF16 [M,6144]")
-    lib = _lib.load()
     n, dev = x.shape[0], x.device
     sw = w.shared_weights
     shared = None
@@ -448,44 +458,42 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
         from .shared_expert import shared_expert_parallel
         current = torch.cuda.current_stream(dev)
         shared = shared_expert_parallel(x, sw, current)
-    logits = _logits(x, w, router_logits)
-    if sw is not None:
-        return _with_shared(x, w, logits, shared, return_partials)
-    if logits.ndim == 3:
-        # split-K partials from the router GEMM: the top-4 kernel adds them in split order, then the stages run one by one
-        wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
-        sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
-        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w, prefetch_next=True)
-        slots = grouped_gemm2(hq, sfh, sort, w)
-        return (slots, None) if return_partials else reduce_slots(slots)
-    ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     slots = torch.empty((n, TOPK, H), dtype=torch.bfloat16, device=dev)
-    out = None if return_partials else torch.empty((n, H), dtype=torch.bfloat16, device=dev)
-    _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
-                                   _ptr(slots), _ptr(out), _ptr(status_word(dev)), _stream(dev)), "forward")
-    return (slots, None) if return_partials else out
-
-
-def _with_shared(x, w, logits, shared, return_partials):
-    """The routed slots on the current stream, then the join with the side stream and the reduce with the shared term."""
-    lib = _lib.load()
-    n, dev = x.shape[0], x.device
-    if logits.ndim == 3:
-        wt, ids = topk_route(logits, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
-        sort = moe_sort(ids, wt, variant_for(n), w.num_experts)
-        hq, sfh = grouped_gemm1(*quant_dispatch(x, sort), sort, w, prefetch_next=True)
-        slots = grouped_gemm2(hq, sfh, sort, w)
-    else:
-        ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
-        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        slots = torch.empty((n, TOPK, H), dtype=torch.bfloat16, device=dev)
-        _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
-                                       _ptr(slots), None, _ptr(status_word(dev)), _stream(dev)), "forward")
+    out = None if (return_partials or sw is not None) else torch.empty((n, H), dtype=torch.bfloat16, device=dev)
+    _routed_layer(x, w, router_logits, slots, out)
+    if sw is None:
+        return (slots, None) if return_partials else out
     current = torch.cuda.current_stream(dev)
-    current.wait_stream(w.shared_weights.stream)
+    current.wait_stream(sw.stream)
     shared.record_stream(current)
     return (slots, shared) if return_partials else reduce_slots(slots, shared)
+
+
+def _routed_layer(x, w, router_logits, slots, out):
+    """One C-ABI call for the routed layer on the current stream: ``b200moe_forward`` when the caller hands fp32 logits,
+    ``b200moe_forward_x`` (router GEMM fused with the input quantiser inside the call) when it hands only ``x``."""
+    lib = _lib.load()
+    n, dev = x.shape[0], x.device
+    if router_logits is not None:
+        if router_logits.shape != (n, w.num_experts) or router_logits.dtype != torch.float32:
+            raise ValueError(f"router_logits: expected fp32 [{n}, {w.num_experts}]")
+        logits = router_logits.contiguous()
+        ws_bytes = int(lib.b200moe_workspace_bytes(n, w.num_experts))
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        _lib.check(lib.b200moe_forward(ctypes.byref(w.abi()), _ptr(x), _ptr(logits), n, _ptr(workspace), ws_bytes,
+                                       _ptr(slots), _ptr(out), _ptr(status_word(dev)), _stream(dev)), "forward")
+        return
+    if w.router_weight is None:
+        raise ValueError("needs router_logits= or MoeWeights with router_weight")
+    ws_bytes = int(lib.b200moe_workspace_bytes_x(n, w.num_experts))
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    _lib.check(lib.b200moe_forward_x(ctypes.byref(w.abi()), _ptr(x), n, _ptr(workspace), ws_bytes, _ptr(slots), _ptr(out),
+                                     _ptr(status_word(dev)), _stream(dev)), "forward_x")
+
+
+def set_wait_limit_ns(ns: int) -> None:
+    """How long a device-side wait may last on the current device before the kernel gives up with status 1 (default 2 s)."""
+    _lib.check(_lib.load().b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
 
 
 WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000)  # one-launch GEMMs, one size per block height, the two-CTA GEMM1
@@ -501,6 +509,8 @@ def warm_up_mxfp4_moe(w, *, partials=False, workers=None):
             x = torch.zeros((m, H), device=dev, dtype=torch.bfloat16)
             lg = torch.zeros((m, w.num_experts), device=dev, dtype=torch.float32)
             mxfp4_moe(x, w, return_partials=False, router_logits=lg)
+            if w.router_weight is not None:
+                mxfp4_moe(x, w, return_partials=False)
             if partials:
                 mxfp4_moe(x, w, return_partials=True, router_logits=lg)
     torch.cuda.synchronize(dev)

@@ -15,10 +15,16 @@ on CPU tensors too, which is how the world_size-2 gloo tests exercise it without
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
-import torch
-import torch.distributed as dist
+# Only plain peer pointers are taken from torch's symmetric memory. Its rendezvous would otherwise also bind the buffers
+# to an NVLink multicast object on NVSwitch machines, and a rank that ends while its memory is bound to one can raise
+# NVLink faults on the other ranks' GPUs. Must be set before the first symmetric-memory use in the process.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 H, I, E, TOPK = 6144, 768, 128, 4  # noqa: E741
 
@@ -176,7 +182,12 @@ class ExpertParallelMoe:
         tokens = x.shape[0]
         chain.variant_for(tokens)
         wt, ids = chain.topk_route(router_logits, self.bias, self.scale, self.mode)
-        if self.peer is not None and tokens * TOPK <= self.peer.max_pairs:
+        if self.peer is not None:
+            # every rank must take the same branch (the two forms issue different collectives): the slot buffers were
+            # sized at construction, so a batch that does not fit is an error here, not a silent change of path
+            if tokens * TOPK > self.peer.max_pairs:
+                raise ValueError(f"{tokens} tokens exceed the peer slot buffer ({self.peer.max_pairs // TOPK} tokens): "
+                                 "construct ExpertParallelMoe with a larger peer_pairs")
             return self._forward_peer(x, wt, ids, return_partials)
         codes, scales = chain.mxfp4_quant(x)
         # where every pair goes; the row counts cross the ranks and reach the host in one read

@@ -24,20 +24,42 @@ def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-def _check(fields, device):
-    for tensor, shape, dtype in fields:
-        if (not isinstance(tensor, torch.Tensor) or tuple(tensor.shape) != shape or tensor.dtype != dtype
-                or not tensor.is_contiguous() or tensor.device != device):
-            raise ValueError(f"expected contiguous {dtype} {shape} on {device}")
+# Every payload field of the two input types: (row width, dtype). A payload is valid when each of its fields is a
+# contiguous [M, width] tensor of that dtype on the layer's device, with one M for all of them.
+_FIELDS = {
+    "routed_codes": (H // 2, torch.uint8), "routed_scales": (H // 32, torch.uint8),
+    "topk_weights": (TOPK, torch.float32), "topk_ids": (TOPK, torch.int32),
+    "shared_codes": (H, torch.uint8), "shared_scales": (H // 32, torch.uint8),
+    "correction_mask": (H // 8, torch.uint8),
+}
+
+
+def _rows_of(obj, anchor):
+    """Token count of a payload, read from its ``anchor`` field; ValueError when that field is no [M, width] tensor or M is
+    outside the range the entry serves."""
+    from .chain import variant_for
+    t = getattr(obj, anchor)
+    if not isinstance(t, torch.Tensor) or t.ndim != 2:
+        raise ValueError(f"{anchor}: expected a row-major [M, {_FIELDS[anchor][0]}] tensor")
+    variant_for(t.shape[0])
+    return t.shape[0]
+
+
+def _require(obj, names, rows, device):
+    for name in names:
+        width, dtype = _FIELDS[name]
+        t = getattr(obj, name)
+        if (not isinstance(t, torch.Tensor) or tuple(t.shape) != (rows, width) or t.dtype != dtype
+                or not t.is_contiguous() or t.device != device):
+            raise ValueError(f"{name}: expected contiguous {dtype} [{rows}, {width}] on {device}")
 
 
 @dataclass(frozen=True)
 class MoeInput:
-    """Quantised operands and routing, no bf16 activations or expert weights (reference prepared_input.py:15-76).
-
-    ``tensors()`` returns the gather payload in constructor order, without copies. The scales are e8m0 bytes per 32
-    values, the routing weights include the routed scaling factor; the shared payloads are the shared expert's MXFP8
-    input (None for a layer without one)."""
+    """What the routed experts and the shared expert need from a token, and nothing else: its MXFP4 codes and scales, its
+    top-4 routing (weights already times the routed scaling factor) and, for a layer with a shared expert, its MXFP8 codes
+    and scales. Field order is the schema of the reference's type (prepared_input.py:15-36) so payloads interchange;
+    ``tensors()`` hands the fields out in that order without copying."""
     routed_codes: torch.Tensor
     routed_scales: torch.Tensor
     topk_weights: torch.Tensor
@@ -50,43 +72,37 @@ class MoeInput:
                 self.shared_scales)
 
     def compact(self):
-        """The 7328 B/token payload (packing costs a launch); release this object's FP4 codes after packing."""
+        """Drops the 3072 bytes of FP4 codes per token in favour of a 768-byte correction mask (one kernel launch):
+        7328 bytes per token to gather instead of 9632. Needs the shared expert's operands, from which the codes are
+        rebuilt (reference prepared_input.py:38-51)."""
         if self.shared_codes is None or self.shared_scales is None:
             raise ValueError("compact input requires shared MXFP8 operands")
-        if not isinstance(self.routed_codes, torch.Tensor) or self.routed_codes.ndim != 2:
-            raise ValueError("expected routed codes [M,3072]")
-        n = self.routed_codes.shape[0]
-        partial = MoeInputCompact(self.routed_scales, self.topk_weights, self.topk_ids, self.shared_codes,
-                                  self.shared_scales, None)
-        partial._validate(check_mask=False)
-        dev = self.shared_codes.device
-        _check(((self.routed_codes, (n, H // 2), torch.uint8),), dev)
-        mask = torch.empty((n, H // 8), dtype=torch.uint8, device=dev)
+        n = _rows_of(self, "routed_codes")
+        dev = self.routed_codes.device
+        if dev.type != "cuda":
+            raise ValueError("compact input requires CUDA operands")
+        _require(self, ("routed_codes", "routed_scales", "topk_weights", "topk_ids", "shared_codes", "shared_scales"), n, dev)
+        mask = torch.empty((n, _FIELDS["correction_mask"][0]), dtype=torch.uint8, device=dev)
         _lib.check(_lib.load().b200moe_sidecar_pack(_ptr(self.routed_codes), _ptr(self.routed_scales),
                                                     _ptr(self.shared_codes), _ptr(self.shared_scales), n, _ptr(mask),
                                                     _stream(dev)), "sidecar_pack")
-        return MoeInputCompact(*partial.tensors()[:-1], mask)
+        return MoeInputCompact(self.routed_scales, self.topk_weights, self.topk_ids, self.shared_codes, self.shared_scales,
+                               mask)
 
     def validate(self, w):
-        from .chain import variant_for
-        if not isinstance(self.routed_codes, torch.Tensor) or self.routed_codes.ndim != 2:
-            raise ValueError("routed_codes must be row-major [M,3072]")
-        n = self.routed_codes.shape[0]
-        variant_for(n)
-        dev = w.w13.device
-        fields = [(self.routed_codes, (n, H // 2), torch.uint8), (self.routed_scales, (n, H // 32), torch.uint8),
-                  (self.topk_weights, (n, TOPK), torch.float32), (self.topk_ids, (n, TOPK), torch.int32)]
+        """ValueError unless every field the layer ``w`` reads is present with the right shape, dtype and device."""
+        n = _rows_of(self, "routed_codes")
+        names = ["routed_codes", "routed_scales", "topk_weights", "topk_ids"]
         if w.shared_weights is not None:
-            fields += [(self.shared_codes, (n, H), torch.uint8), (self.shared_scales, (n, H // 32), torch.uint8)]
-        _check(fields, dev)
+            names += ["shared_codes", "shared_scales"]
+        _require(self, names, n, w.w13.device)
 
 
 @dataclass(frozen=True)
 class MoeInputCompact:
-    """The lossless gather payload, in ``tensors()`` order, all row-major (reference prepared_input.py:79-114): the FP4
-    scales and one correction bit per value rebuild the direct FP4 codes from the shared FP8 ones (signed zero and the
-    quantisation kept): 2304 B/token less than ``MoeInput`` with a shared expert, at one launch to pack and one to
-    rebuild."""
+    """``MoeInput`` without the FP4 codes: the FP4 scales plus one bit per value say how each FP4 code differs from the
+    one the FP8 code would give, so ``expand`` restores the codes exactly, signed zeros included. Same field order as the
+    reference's type (prepared_input.py:79-96); 2304 bytes per token smaller on the wire."""
     routed_scales: torch.Tensor
     topk_weights: torch.Tensor
     topk_ids: torch.Tensor
@@ -98,28 +114,18 @@ class MoeInputCompact:
         return (self.routed_scales, self.topk_weights, self.topk_ids, self.shared_codes, self.shared_scales,
                 self.correction_mask)
 
-    def _validate(self, *, check_mask=True):
-        from .chain import variant_for
-        if not isinstance(self.shared_codes, torch.Tensor) or self.shared_codes.ndim != 2:
-            raise ValueError("expected shared codes [M,6144]")
-        n = self.shared_codes.shape[0]
-        if self.shared_codes.device.type != "cuda":
-            raise ValueError("compact input requires CUDA operands")
-        variant_for(n)
-        specs = (((n, H // 32), torch.uint8), ((n, TOPK), torch.float32), ((n, TOPK), torch.int32), ((n, H), torch.uint8),
-                 ((n, H // 32), torch.uint8), ((n, H // 8), torch.uint8))
-        tensors = self.tensors() if check_mask else self.tensors()[:-1]
-        _check([(t, shape, dtype) for t, (shape, dtype) in zip(tensors, specs)], self.shared_codes.device)
-
     def expand(self) -> MoeInput:
-        """Reconstruct the FP4 codes bit for bit; keep routing, scales and shared codes."""
-        self._validate()
-        n, dev = self.shared_codes.shape[0], self.shared_codes.device
-        q = torch.empty((n, H // 2), dtype=torch.uint8, device=dev)
+        """The full ``MoeInput`` again (one kernel launch writes the FP4 codes; every other field is shared, not copied)."""
+        n = _rows_of(self, "shared_codes")
+        dev = self.shared_codes.device
+        if dev.type != "cuda":
+            raise ValueError("compact input requires CUDA operands")
+        _require(self, ("routed_scales", "topk_weights", "topk_ids", "shared_codes", "shared_scales", "correction_mask"), n, dev)
+        codes = torch.empty((n, _FIELDS["routed_codes"][0]), dtype=torch.uint8, device=dev)
         _lib.check(_lib.load().b200moe_sidecar_unpack(_ptr(self.correction_mask), _ptr(self.routed_scales),
-                                                      _ptr(self.shared_codes), _ptr(self.shared_scales), n, _ptr(q),
+                                                      _ptr(self.shared_codes), _ptr(self.shared_scales), n, _ptr(codes),
                                                       _stream(dev)), "sidecar_unpack")
-        return MoeInput(q, self.routed_scales, self.topk_weights, self.topk_ids, self.shared_codes, self.shared_scales)
+        return MoeInput(codes, self.routed_scales, self.topk_weights, self.topk_ids, self.shared_codes, self.shared_scales)
 
 
 def prepare_mxfp4_moe(x, w) -> MoeInput:
@@ -161,20 +167,18 @@ def mxfp4_moe_prepared(x, w, *, return_partials):
 
 
 def gather_mxfp4_moe(local: MoeInput, comm) -> MoeInputCompact:
-    """A prepared shard gathered losslessly (compact) for the same public MoE entry (reference prepared_input.py:190-209).
-    ``comm``: the ``torch.distributed`` process group (NCCL) of the ranks that share the sequence; every rank supplies the
-    same positive row count, zero padding included. The result holds the rows of all ranks in rank order."""
+    """All ranks of ``comm`` (a ``torch.distributed`` process group over NCCL) contribute their prepared shard and receive
+    every rank's rows, rank 0's first, in the compact form (the role of reference prepared_input.py:190-209). Each rank
+    brings the same number of rows (pad with zero rows where needed); a layer without a shared expert cannot use the compact
+    form and is refused."""
     import torch.distributed as dist
     if not isinstance(local, MoeInput):
         raise ValueError("expected an explicit prepared MoeInput")
     if local.shared_codes is None or local.shared_scales is None:
         raise ValueError("lossless mixed-format gather requires shared MXFP8 operands")
-    compact = local.compact()
-    world = dist.get_world_size(comm)
-    rows = local.routed_codes.shape[0]
-    outs = []
-    for t in compact.tensors():
-        out = torch.empty((world * rows, *t.shape[1:]), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, t, group=comm)
-        outs.append(out)
-    return MoeInputCompact(*outs)
+    fields = local.compact().tensors()
+    ranks = dist.get_world_size(comm)
+    gathered = [f.new_empty((ranks * f.shape[0],) + tuple(f.shape[1:])) for f in fields]
+    for dst, src in zip(gathered, fields):
+        dist.all_gather_into_tensor(dst, src, group=comm)
+    return MoeInputCompact(*gathered)

@@ -17,6 +17,22 @@ RECORD_BYTES = 17408
 
 _side_streams: dict = {}
 
+# Inside a dual-batch-overlap microbatch the shared expert stays on the caller's stream (the server already overlaps one
+# microbatch's compute with the other's collectives). A server hands over its query with ``set_dbo_query``; without one
+# the module constant ``DBO`` answers (reference shared_expert.py:30-44).
+DBO = False
+_dbo_query = None
+
+
+def set_dbo_query(query) -> None:
+    """``query()`` tells whether the current call runs inside a DBO microbatch; ``None`` goes back to ``DBO``."""
+    global _dbo_query
+    _dbo_query = query
+
+
+def in_dbo() -> bool:
+    return bool(_dbo_query()) if _dbo_query is not None else DBO
+
 
 def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
@@ -149,5 +165,7 @@ def shared_expert(x: torch.Tensor | None, w: SharedWeights, *, x_quant=None, str
 def shared_expert_parallel(x, w: SharedWeights, current, **kwargs):
     """``shared_expert`` on ``w.stream`` (the device's side stream) after the work queued on ``current`` so far
     (reference shared_expert.py:94-101). The caller makes ``current`` wait for ``w.stream`` before reading the result."""
+    if in_dbo():  # a DBO microbatch: no side stream (``current.wait_stream(w.stream)`` afterwards is then a no-op)
+        return shared_expert(x, w, stream=current, **kwargs)
     w.stream.wait_stream(current)
     return shared_expert(x, w, stream=w.stream, **kwargs)

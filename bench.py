@@ -3,16 +3,18 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl reference] [--no-sweep]
 
 One "step" is one pass of the layer over one batch of T synthetic tokens (route, quantise, sort, gather, GEMM1 + SwiGLU +
-requantisation, GEMM2 x routing weight, slot reduce). At N=1 the headline workload is the decode configuration at its
-largest size, T=256 (all 128 experts active, 963 MB of weights streamed per step); the other decode and prefill sizes are
-reported under "sweep". At N>1 the 128 experts are sharded over the ranks (expert parallel, NCCL all-to-all dispatch and
-combine) and the workload is T=16384 tokens split evenly over the ranks, fixed total work ("strong" scaling).
+requantisation, GEMM2 x routing weight, slot reduce). The workload is the same at every N: T=16384 tokens (the
+expert-parallel configuration), on one GPU with all 128 experts at N=1 and split evenly over the ranks with the experts
+sharded (expert parallel, dispatch and combine over NVLink) at N>1 -- fixed total work, "strong" scaling. The decode
+(T=1..256) and prefill (T=2048, 8192) configurations are reported under "sweep", and the dominant decode kernel (GEMM1 at
+T=256, HBM-bound) keeps its own roofline block, "roofline_decode".
 
-Timing: every step is a CUDA-graph replay of the whole-layer C-ABI call (b200moe_forward) on one of 8 rotating inputs,
-timed with CUDA events on the launching stream; between steps a 512 MB buffer is overwritten so nothing of the previous
-step survives in L2. "e2e" times the host-buffer C-ABI call (b200moe_forward_host): pinned host input -> device, the
-layer, device -> host output, per step. "cpu_baseline" / --impl reference time the CPU oracle (a numpy port of the
-reference's torch oracle) on the box's host cores on a 16-token sample of the same workload.
+Timing: every step is a CUDA-graph replay of the whole-layer C-ABI call (b200moe_forward) on one of the rotating inputs,
+timed with CUDA events on the launching stream; before every step, untimed, a 512 MB buffer is overwritten and another
+384 MB read, so the step starts on a cold and clean L2. "e2e" times the host-buffer C-ABI call (b200moe_forward_host):
+pinned host input -> device, the layer, device -> host output, per step. "cpu_baseline" / --impl reference time the
+reference's CPU path on the box's host cores on a stated sample of the workload's tokens: the reference's own torch
+oracle file when a copy travels with the repository (kind "reference"), else the numpy restatement (kind "port").
 """
 from __future__ import annotations
 
@@ -39,12 +41,18 @@ NOMINAL_HBM_GBS, NOMINAL_FP4_TFLOPS = 8000.0, 9000.0
 DECODE_SWEEP = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 PREFILL_SWEEP = (2048, 8192)
 N_INPUTS = 8
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch at T=256, from the ncu capture summarised under
-# profiles/ (None until a capture exists)
-# profiles/grouped_gemm_t256_ncu_full.md: 679,282,176 read + 4,750,336 written by the layer's GEMM1 launch, which also
-# asks L2 for 592 W2 tiles (30,916,608 bytes) on behalf of the GEMM2 that follows; only valid for the T=256 workload
-NCU_GEMM1_TRAFFIC_BYTES = 684_032_512
-NCU_GEMM1_PREFETCH_BYTES = 592 * 3 * 17408
+HEADLINE_TOKENS = 16384
+CPU_SAMPLE_TOKENS = 16
+
+
+def ncu_traffic(tokens):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch from the ncu capture of this workload, as recorded
+    in profiles/ncu_traffic.json by whoever made the capture (null when there is none for this token count)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f).get("gemm1", {}).get(str(tokens))
 
 
 def measured_peaks():
@@ -94,66 +102,99 @@ class ClockSampler:
                 "samples": len(ok)}
 
 
-def cpu_oracle_sample(weights_np, x_bits, logits, repeats=3):
-    """tokens/s of the CPU oracle on a 16-token sample: quantise, route, experts, slot rounding, reduce."""
+def cpu_reference(weights_np, x_bits, logits):
+    """-> (fn, kind): one call of the reference's CPU path on a token sample (quantise, route, experts, slot rounding,
+    reduce). The reference's own torch file is used when a copy sits in baseline/_ref/ (git-ignored; the build step copies
+    it there where the reference checkout exists), else the numpy restatement."""
     from oracle import moe_oracle as orc
-    sample = min(16, x_bits.shape[0])
-    xs, lg = x_bits[:sample], logits[:sample]
-    orc.moe_layer(xs, lg, *weights_np)  # warm
+    path = os.path.join(ROOT, "baseline", "_ref", "mxfp4_moe_reference.py")
+    if os.path.exists(path):
+        import importlib.util
+        import torch
+        spec = importlib.util.spec_from_file_location("mxfp4_moe_reference", path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        torch.set_num_threads(os.cpu_count())
+        tw = [torch.from_numpy(a) for a in weights_np]
+        x = torch.from_numpy(orc.bf16_to_f32(x_bits))
+        lg = torch.from_numpy(logits)
+
+        def call():
+            xq, xs = ref.mxfp4_quant_ref(x)
+            top = torch.topk(lg, 4, dim=1)
+            wt = torch.softmax(top.values, dim=1)
+            out = ref.w4a4_moe_ref((xq, xs), *tw, wt, top.indices.int())
+            return out
+        return call, "reference"
+    return (lambda: orc.moe_layer(x_bits, logits, *weights_np)), "port"
+
+
+def cpu_sample(weights_np, x_bits, logits, repeats):
+    call, kind = cpu_reference(weights_np, x_bits[:CPU_SAMPLE_TOKENS], logits[:CPU_SAMPLE_TOKENS])
+    call()  # warm
     times = []
     for _ in range(repeats):
         t0 = time.perf_counter()
-        orc.moe_layer(xs, lg, *weights_np)
+        call()
         times.append(time.perf_counter() - t0)
-    med = statistics.median(times)
-    return sample / med, med, sample
+    return times, kind
 
 
 def reference_arm(args):
-    """--impl reference: the CPU implementation of the path (the oracle port; the reference's own torch file does not
-    travel to the GPU box) on the host cores, each step a 16-token sample of the workload."""
+    """--impl reference: the reference's CPU implementation of the path on the host cores (see cpu_reference), each step
+    one call on a 16-token sample of the workload's tokens (all 128 experts' weights resident)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import moe_oracle as orc
     weights_np, gen = orc.make_weights(seed=0)
-    tokens = args.tokens or (256 if args.gpus == 1 else 16384)
-    x_bits, logits = orc.make_inputs(gen, 16)
+    tokens = args.tokens or HEADLINE_TOKENS
+    x_bits, logits = orc.make_inputs(gen, CPU_SAMPLE_TOKENS)
+    call, kind = cpu_reference(weights_np, x_bits, logits)
     for _ in range(max(args.warmup, 1)):
-        orc.moe_layer(x_bits, logits, *weights_np)
+        call()
     times = []
     for _ in range(args.steps):
         t0 = time.perf_counter()
-        orc.moe_layer(x_bits, logits, *weights_np)
+        call()
         times.append(time.perf_counter() - t0)
     per_step = sum(times) / len(times)
-    value = 16 / per_step
+    value = CPU_SAMPLE_TOKENS / per_step
     cores = os.cpu_count()
+    cfg = workload_config(tokens, args.gpus)
+    cfg["cpu_sample_tokens"] = CPU_SAMPLE_TOKENS
     line = {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
-            "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
-            "dtype": "mxfp4", "data": "synthetic",
-            "config": workload_config(tokens, args.gpus),
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                             "sample": "16 tokens of the workload per step, all 128 experts' weights resident, numpy + BLAS threads"},
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "mxfp4", "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind,
+                             "sample": f"{CPU_SAMPLE_TOKENS} of the workload's {tokens} tokens per step (tokens/s = "
+                                       f"{CPU_SAMPLE_TOKENS} / step time), all 128 experts' weights resident, "
+                                       + ("the reference's torch oracle, torch threads = cores" if kind == "reference"
+                                          else "numpy restatement of the reference's torch oracle, BLAS threads")},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 def workload_config(tokens, gpus):
     return {"workload": f"mxfp4_h6144_i768_e128_top4 routed MoE layer, T={tokens}"
-                        + (" decode (configuration 1)" if gpus == 1 and tokens <= 256 else ""),
+                        + (" (the expert-parallel configuration's token count; fits one GPU)" if tokens == HEADLINE_TOKENS else ""),
             "tokens": tokens, "hidden": H, "intermediate": I, "experts": E, "top_k": TOPK, "routing": "softmax top-4 renormalised",
             "weights": "E2M1 codes uniform, E8M0 scales 2^-7..2^-3, seed 0", "activations": "bf16 N(0,1), logits fp32 N(0,1)",
             "parallelism": "single GPU" if gpus == 1 else f"expert parallel ep{gpus}, {E // gpus} experts per GPU",
-            "l2": L2_NOTE + ("; 8 rotating inputs" if gpus == 1 else "; 4 rotating inputs per rank"),
+            "l2": L2_NOTE + (f"; {rotating_inputs(tokens)} rotating inputs" if gpus == 1 else "; 4 rotating inputs per rank"),
             "timing": "CUDA-graph replay of the whole-layer C-ABI call, CUDA events per step"}
+
+
+def rotating_inputs(tokens):
+    return N_INPUTS if tokens <= 8192 else 4
 
 
 class Layer:
     """Device buffers for one token count and the graphs that replay the C-ABI call on each rotating input."""
 
-    def __init__(self, w, tokens, lib, chain, torch, n_inputs=N_INPUTS, seed=1234):
+    def __init__(self, w, tokens, lib, chain, torch, n_inputs=None, seed=1234):
+        n_inputs = rotating_inputs(tokens) if n_inputs is None else n_inputs
         self.tokens, self.lib, self.torch, self.w = tokens, lib, torch, w
         dev = w.w13.device
         g = torch.Generator(device=dev).manual_seed(seed + tokens)
@@ -194,6 +235,9 @@ class Layer:
         # up to 32 tokens: route+sort, quantise+gather, both GEMMs in one launch, reduce; above: routing and sort apart
         # (plus a count pass above 256), quantise+gather, two GEMMs, reduce
         return 4 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
+
+    def replay(self, i):
+        self.graphs[i % len(self.graphs)].replay()
 
 
 class L2Flush:
@@ -279,6 +323,76 @@ def layer_report(tokens, ms, e_active, peaks):
             "frac_of_measured_roofline": roof_meas / t, "frac_of_nominal_roofline": roof_nom / t}
 
 
+def gemm_times(torch, chain, w, layer, flush, args):
+    """The two grouped GEMM launches of one layer call, each timed alone (CUDA events, cold clean L2 before every launch)."""
+    wt, ids = chain.topk_route(layer.logits[0], None, 1.0, "softmax")
+    sb = chain.moe_sort(ids, wt, chain.variant_for(layer.tokens))
+    xs, sfx = chain.dispatch_rows(chain.mxfp4_quant(layer.x[0]), sb)
+    g1 = time_steps(torch, lambda i: chain.grouped_gemm1(xs, sfx, sb, w), args.steps, args.warmup, flush)
+    hq, sfh = chain.grouped_gemm1(xs, sfx, sb, w)
+    g2 = time_steps(torch, lambda i: chain.grouped_gemm2(hq, sfh, sb, w, slots=layer.slots), args.steps, args.warmup, flush)
+    return {"g1_ms": sum(g1) / len(g1), "g2_ms": sum(g2) / len(g2), "rows": int(sb.num_valid[0]), "bm": sb.bm,
+            "experts": int(ids.unique().numel())}
+
+
+def gemm1_hbm_roofline(tokens, k, peaks):
+    """GEMM1 against the HBM roofline: its algorithmic bytes (the active experts' W13 codes and scales once, the sorted
+    rows' codes and scales in, the h codes and scales out) over its launch time, over the measured copy bandwidth."""
+    byts = k["experts"] * W13_BYTES + k["rows"] * (H // 2 + H // 32) + k["rows"] * (I // 2 + I // 32)
+    gbs = byts / (k["g1_ms"] * 1e-3) / 1e9
+    g2_bytes = k["experts"] * (EXPERT_BYTES - W13_BYTES) + k["rows"] * 408 + tokens * 4 * H * 2
+    return {"kernel": f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)", "tokens": tokens,
+            "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "peak_source": peaks["source"] + " (STREAM-style copy)", "algorithmic_bytes": byts,
+            "us_per_launch": k["g1_ms"] * 1e3, "traffic": ncu_traffic(tokens),
+            "gemm2_us_per_launch": k["g2_ms"] * 1e3, "gemm2_achieved": g2_bytes / (k["g2_ms"] * 1e-3) / 1e9}
+
+
+def gemm1_tensor_roofline(tokens, k, peaks):
+    """GEMM1 against the tensor roofline: 2 * 6144 * 1536 flops for each of the 4T routed (token, slot) rows (padding rows
+    are not algorithmic work) over its launch time, over 4 x the measured dense bf16 rate (the file of measured peaks has no
+    FP4 figure; 4 is the nominal ratio of block-scaled FP4 to bf16 on this part)."""
+    flops = 4 * tokens * 2 * H * 2 * I
+    tf = flops / (k["g1_ms"] * 1e-3) / 1e12
+    peak = 4 * peaks["bf16_tflops"]
+    g2_tf = 4 * tokens * 2 * I * H / (k["g2_ms"] * 1e-3) / 1e12
+    return {"kernel": f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)", "tokens": tokens,
+            "bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+            "peak_source": "4 x " + peaks["source"] + " dense bf16 (burst), the nominal FP4:bf16 ratio",
+            "algorithmic_flops": flops, "sorted_rows_incl_padding": k["rows"], "us_per_launch": k["g1_ms"] * 1e3,
+            "traffic": ncu_traffic(tokens), "gemm2_us_per_launch": k["g2_ms"] * 1e3, "gemm2_achieved": g2_tf,
+            "hbm_view": {kk: v for kk, v in gemm1_hbm_roofline(tokens, k, peaks).items() if kk in ("achieved", "frac", "algorithmic_bytes")}}
+
+
+def entry_with_router(torch, chain, w, flush, args, sizes=(256, 2048, 8192)):
+    """The call a server makes -- mxfp4_moe(x, w) with the router inside (b200moe_forward_x) -- beside the same call fed
+    with precomputed logits, as CUDA-graph replays."""
+    gate = torch.randn((E, H), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)) / H ** 0.5
+    wg = chain.MoeWeights(gate, None, w.w13, None, w.w2, None, w.routed_scaling_factor, w.routing_mode)
+    out = []
+    with torch.inference_mode():
+        for tokens in sizes:
+            g = torch.Generator(device="cuda").manual_seed(77 + tokens)
+            xs = [torch.randn((tokens, H), device="cuda", generator=g).bfloat16() for _ in range(4)]
+            lgs = [(x.float() @ gate.t()).contiguous() for x in xs]
+            chain.mxfp4_moe(xs[0], wg)
+            torch.cuda.synchronize()
+            graphs = {"x_only": [], "with_logits": []}
+            keep = []
+            for x, lg in zip(xs, lgs):
+                for name, kw in (("x_only", {}), ("with_logits", {"router_logits": lg})):
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        keep.append(chain.mxfp4_moe(x, wg, **kw))
+                    graphs[name].append(gr)
+            t = {name: time_steps(torch, lambda i, L=lst: L[i % len(L)].replay(), args.steps, args.warmup, flush)
+                 for name, lst in graphs.items()}
+            out.append({"tokens": tokens, "x_only_us": sum(t["x_only"]) / len(t["x_only"]) * 1e3,
+                        "with_logits_us": sum(t["with_logits"]) / len(t["with_logits"]) * 1e3})
+            del graphs, keep, xs, lgs
+    return out
+
+
 def single_gpu(args):
     import torch
     from amd_kernels_b200 import _lib
@@ -288,38 +402,33 @@ def single_gpu(args):
     lib = _lib.load()
     peaks = measured_peaks()
     weights_np, gen = orc.make_weights(seed=0)
-    x0_bits, lg0 = orc.make_inputs(gen, 16)
+    x0_bits, lg0 = orc.make_inputs(gen, CPU_SAMPLE_TOKENS)
     w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(a).cuda() for a in weights_np),
                                         routing_mode="softmax", routed_scaling_factor=1.0)
     chain.warm_up_mxfp4_moe(w)
     flush = L2Flush(torch)
-    headline_t = args.tokens or 256
+    headline_t = args.tokens or HEADLINE_TOKENS
+    decode_t = 256
     sweep_ts = [headline_t] if args.no_sweep else sorted(set(DECODE_SWEEP + PREFILL_SWEEP + (headline_t,)))
-    sweep, layers = [], {}
+    sweep, keep = [], {}
     clocks = ClockSampler(torch.cuda.current_device())
     with clocks:
         for tokens in sweep_ts:
             layer = Layer(w, tokens, lib, chain, torch)
             layer.capture()
-            ms = time_steps(torch, lambda i, L=layer: L.graphs[i % N_INPUTS].replay(), args.steps, args.warmup, flush)
+            ms = time_steps(torch, layer.replay, args.steps, args.warmup, flush)
             rep = layer_report(tokens, sum(ms) / len(ms), layer.active_experts(chain), peaks)
             rep["us_min"] = min(ms) * 1e3
             sweep.append(rep)
             if tokens == headline_t:
-                layers[tokens] = layer
                 head_ms = ms
+            if tokens in (headline_t, decode_t):
+                keep[tokens] = gemm_times(torch, chain, w, layer, flush, args)
+            if tokens == headline_t:
+                head = layer
             else:
                 del layer
-        layer = layers[headline_t]
-        # ---- the dominant kernel alone: grouped GEMM1 (+SwiGLU + requantisation)
-        wt, ids = chain.topk_route(layer.logits[0], None, 1.0, "softmax")
-        sb = chain.moe_sort(ids, wt, chain.variant_for(headline_t))
-        xs, sfx = chain.dispatch_rows(chain.mxfp4_quant(layer.x[0]), sb)
-        g1 = time_steps(torch, lambda i: chain.grouped_gemm1(xs, sfx, sb, w), args.steps, args.warmup, flush)
-        hq, sfh = chain.grouped_gemm1(xs, sfx, sb, w)
-        g2 = time_steps(torch, lambda i: chain.grouped_gemm2(hq, sfh, sb, w, slots=layer.slots), args.steps, args.warmup, flush)
-        rows = int(sb.num_valid[0])
-        e_act = int(ids.unique().numel())
+        layer = head
         # ---- end to end through the host-buffer C-ABI call
         hx = [t.cpu().pin_memory() for t in layer.x]
         hl = [t.cpu().pin_memory() for t in layer.logits]
@@ -328,7 +437,7 @@ def single_gpu(args):
         p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
 
         def e2e_step(i):
-            j = i % N_INPUTS
+            j = i % len(hx)
             _lib.check(lib.b200moe_forward_host(ctypes.byref(w.abi()), p(hx[j]), p(hl[j]), headline_t, p(dx), p(dl),
                                                 p(layer.workspace), layer.ws_bytes, p(layer.slots), p(layer.out), p(hout),
                                                 p(layer.status), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
@@ -343,34 +452,32 @@ def single_gpu(args):
             torch.cuda.current_stream().synchronize()  # the caller reads the result before the next step
         e2e_wall = time.perf_counter() - t0
         e2e_ms = time_steps(torch, e2e_step, args.steps, 1, flush)
-        shared_rep = with_shared_expert(torch, chain, orc, w, layer, flush, args)
+        shared_rep = None if args.no_sweep else with_shared_expert(torch, chain, orc, w, layer, flush, args)
+        router_rep = None if args.no_sweep else entry_with_router(torch, chain, w, flush, args)
     status = chain.last_status()
     if status:
         raise RuntimeError(f"device status {status}: a kernel wait timed out")
     ms_per_step = sum(head_ms) / len(head_ms)
-    g1_ms = sum(g1) / len(g1)
-    g1_bytes = e_act * W13_BYTES + rows * (H // 2 + H // 32) + rows * (I // 2 + I // 32)
-    cpu_value, cpu_s, cpu_sample = cpu_oracle_sample(weights_np, x0_bits, lg0)
+    cpu_times, cpu_kind = cpu_sample(weights_np, x0_bits, lg0, repeats=3)
+    cpu_s = statistics.median(cpu_times)
+    head_k = keep[headline_t]
+    tensor_bound = head_k["bm"] == 128 and headline_t * FLOPS_PER_TOKEN / (NOMINAL_FP4_TFLOPS * 1e12) \
+        > (128 * EXPERT_BYTES + headline_t * (4 * H + 4 * E)) / (NOMINAL_HBM_GBS * 1e9)
+    roof = gemm1_tensor_roofline(headline_t, head_k, peaks) if tensor_bound else gemm1_hbm_roofline(headline_t, head_k, peaks)
     line = {"metric": "moe_layer_tokens_per_s", "value": headline_t / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4", "data": "synthetic",
             "config": workload_config(headline_t, 1),
-            "roofline": {"kernel": "grouped_gemm_kernel<1,bm> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)", "bound": "hbm",
-                         "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": g1_bytes / (g1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                         "algorithmic_bytes": g1_bytes, "us_per_launch": g1_ms * 1e3,
-                         "traffic": NCU_GEMM1_TRAFFIC_BYTES if headline_t == 256 else None,
-                         "traffic_includes_l2_prefetch_for_gemm2": NCU_GEMM1_PREFETCH_BYTES if headline_t == 256 else None,
-                         "gemm2_us_per_launch": sum(g2) / len(g2) * 1e3,
-                         "gemm2_achieved": (e_act * (EXPERT_BYTES - W13_BYTES) + rows * 408 + headline_t * 4 * H * 2)
-                         / (sum(g2) / len(g2) * 1e-3) / 1e9},
+            "roofline": roof,
+            "roofline_decode": gemm1_hbm_roofline(decode_t, keep[decode_t], peaks) if decode_t in keep and decode_t != headline_t else None,
             "layer_roofline": next(r for r in sweep if r["tokens"] == headline_t),
-            "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-                             "sample": f"{cpu_sample} tokens (configuration 0), median of 3 calls, {cpu_s:.2f} s per call"},
+            "cpu_baseline": {"value": CPU_SAMPLE_TOKENS / cpu_s, "unit": "tokens/s", "cores": os.cpu_count(), "kind": cpu_kind,
+                             "sample": f"{CPU_SAMPLE_TOKENS} tokens of the workload (tokens/s = {CPU_SAMPLE_TOKENS} / call time), "
+                                       f"median of 3 calls, {cpu_s:.2f} s per call"},
             "e2e": {"value": headline_t / (sum(e2e_ms) / len(e2e_ms) * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": headline_t * (2 * H + 4 * E), "d2h_bytes_per_step": headline_t * 2 * H,
                     "wall_value_with_sync_per_step": headline_t * args.steps / e2e_wall},
-            "with_shared_expert": shared_rep,
+            "with_shared_expert": shared_rep, "entry_with_router": router_rep,
             "gpu_launches": args.steps * layer.launches_per_step(),
             "clocks": clocks.summary(), "sweep": sweep}
     print(json.dumps(line))
@@ -391,7 +498,7 @@ def main():
         return reference_arm(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return single_gpu(args)
-    from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import ep_bench
+    import ep_bench
     return ep_bench.run(args)
 
 

@@ -1,18 +1,26 @@
-"""The multi-GPU leg of bench.py: the expert-parallel layer, one process per GPU under torchrun, NCCL over NVLink.
+"""The multi-GPU leg of bench.py (`python bench.py --gpus N` under torchrun lands here): the expert-parallel layer, one
+process per GPU, NCCL over NVLink.
 
 Workload: global T tokens (default 16384) split evenly over the W ranks; 128/W experts per rank; every step is one
 layer call on every rank (route, quantise, all-to-all dispatch, grouped GEMMs, all-to-all combine, fixed-order reduce).
-Total work is fixed as W grows ("strong" scaling). Per-step device time is taken with CUDA events on each rank after an
-untimed L2 flush (written, then evicted by a read); the job's time is the maximum over the ranks of the summed step times."""
+Total work is fixed as W grows ("strong" scaling; the single-GPU bench line is the same 16384 tokens on one GPU). Per-step
+device time is taken with CUDA events on each rank after an untimed L2 flush (written, then evicted by a read); the job's
+time is the maximum over the ranks of the summed step times. Before anything is timed every rank checks its output on its
+own tokens, bit for bit, against the single-GPU layer with all 128 experts ("parity_checked" in the JSON line)."""
 from __future__ import annotations
 
 import json
 import os
 import time
 
-import numpy as np
-import torch
-import torch.distributed as dist
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # peer pointers only: never bind buffers to a multicast object
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from amd_kernels_b200.moe.mxfp4_h6144_i768_e128_top4 import chain, ep  # noqa: E402
+from bench import ClockSampler, FLOPS_PER_TOKEN, L2Flush, measured_peaks, workload_config  # noqa: E402
 
 H, E, TOPK = 6144, 128, 4
 ROW_BYTES_OUT, ROW_BYTES_IN = 2 * H, H // 2 + H // 32 + 8
@@ -20,26 +28,42 @@ NVLINK_GBS_MEASURED = 770.0  # measured peer-copy bandwidth per direction per GP
 N_INPUTS = 4
 
 
-def build_rank_layer(rank, world, placement, seed=0, peer_pairs=0):
-    from oracle import moe_oracle as orc
-    from . import chain, ep
-    (w13, s13, w2, s2), _ = orc.make_weights(seed=seed)
+def synthetic_weights(seed=0):
+    """The benchmark's checkpoint-layout weights (E2M1 codes uniform over the 16 values, E8M0 scale bytes 120..124), the
+    same generator and seed the single-GPU bench and the tests use."""
+    from oracle import moe_oracle as orc  # data generation only; nothing of the oracle is timed or compared against here
+    return orc.make_weights(seed=seed)[0]
+
+
+def build_layers(rank, world, placement, peer_pairs):
+    """(this rank's expert-parallel layer, the single-GPU layer over all 128 experts used as the parity reference)."""
+    raw = synthetic_weights()
     mine = ep.local_expert_ids(rank, world, placement=placement).numpy()
-    w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(np.ascontiguousarray(a[mine])).cuda()
-                                                     for a in (w13, s13, w2, s2)))
-    del w13, s13, w2, s2
-    return ep.ExpertParallelMoe(w, None, bias=None, routing_mode="softmax", scale=1.0, placement=placement,
-                                peer_pairs=peer_pairs)
+    w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(np.ascontiguousarray(a[mine])).cuda() for a in raw))
+    w_all = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(a).cuda() for a in raw), routing_mode="softmax",
+                                            routed_scaling_factor=1.0)
+    del raw
+    layer = ep.ExpertParallelMoe(w, None, bias=None, routing_mode="softmax", scale=1.0, placement=placement,
+                                 peer_pairs=peer_pairs)
+    return layer, w_all
 
 
-def one_gpu_same_workload(chain, flush, tokens, zipf, steps):
+def check_parity(layer, w_all, xs, lgs):
+    """Every rank: the expert-parallel output on its own tokens == the single-GPU layer on the same tokens, bit for bit.
+    Returns (all ranks equal, mismatching elements summed over the ranks)."""
+    bad = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with torch.inference_mode():
+        for x, lg in zip(xs[:2], lgs[:2]):
+            got = layer.forward(x, lg)
+            want = chain.mxfp4_moe(x, w_all, router_logits=lg)
+            bad += (got.view(torch.int16) != want.view(torch.int16)).sum()
+    dist.all_reduce(bad)
+    return int(bad.item()) == 0, int(bad.item())
+
+
+def one_gpu_same_workload(w, flush, tokens, zipf, steps):
     """Rank 0 alone: the same global token count through the single-GPU layer (all 128 experts on this GPU), timed the
     same way, so the strong-scaling ratio can be read from one JSON line. The other ranks wait at the final barrier."""
-    from oracle import moe_oracle as orc
-    raw, _ = orc.make_weights(seed=0)
-    w = chain.MoeWeights.from_row_major(None, None, *(torch.from_numpy(a).cuda() for a in raw), routing_mode="softmax",
-                                        routed_scaling_factor=1.0)
-    del raw
     gen = torch.Generator(device="cuda").manual_seed(99)
     x = torch.randn((tokens, H), device="cuda", generator=gen).bfloat16()
     lg = torch.randn((tokens, E), device="cuda", generator=gen)
@@ -62,29 +86,43 @@ def one_gpu_same_workload(chain, flush, tokens, zipf, steps):
 
 
 def run(args):
-    from . import chain
+    """One JSON line for the configuration the arguments name; on 8 GPUs without --zipf the skewed-routing configuration
+    (T=4096, Zipf-like logit bias, interleaved expert placement) is measured in the same run and reported under
+    "zipf_t4096" of that line."""
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29511")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
-    tokens_global = args.tokens or 16384
+    zipf = bool(getattr(args, "zipf", False))
+    line = measure(args, rank, world, local, args.tokens or 16384, zipf)
+    if world == 8 and not zipf and not args.tokens:
+        extra = measure(args, rank, world, local, 4096, True)
+        if rank == 0:
+            line["zipf_t4096"] = {k: extra[k] for k in ("value", "unit", "ms_per_step", "config", "roofline", "parity_checked",
+                                                        "parity_mismatching_elements", "one_gpu_same_workload", "clocks")}
+    if rank == 0:
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def measure(args, rank, world, local, tokens_global, zipf):
     if tokens_global % world:
         raise ValueError("the global token count must divide evenly over the ranks")
     t_loc = tokens_global // world
-    zipf = bool(getattr(args, "zipf", False))
     placement = "interleaved" if zipf else "contiguous"
-    layer = build_rank_layer(rank, world, placement, peer_pairs=0 if os.environ.get("B200MOE_EP_COMBINE") == "nccl" else t_loc * TOPK)
+    layer, w_all = build_layers(rank, world, placement, 0 if os.environ.get("B200MOE_EP_COMBINE") == "nccl" else t_loc * TOPK)
     gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
     xs = [torch.randn((t_loc, H), device="cuda", generator=gen).bfloat16() for _ in range(N_INPUTS)]
     lgs = [torch.randn((t_loc, E), device="cuda", generator=gen) for _ in range(N_INPUTS)]
     if zipf:
         skew = -2.2 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
         lgs = [lg + skew for lg in lgs]
-    import sys
-    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))))
-    from bench import ClockSampler, L2Flush, workload_config, FLOPS_PER_TOKEN, measured_peaks
+    parity_ok, parity_bad = check_parity(layer, w_all, xs, lgs)
+    if rank != 0:
+        del w_all
     flush = L2Flush(torch)
     hx = [t.cpu().pin_memory() for t in xs]
     hl = [t.cpu().pin_memory() for t in lgs]
@@ -141,7 +179,7 @@ def run(args):
         link_bytes = mean_rows * remote * (ROW_BYTES_IN + ROW_BYTES_OUT)
         t_link = link_bytes / (NVLINK_GBS_MEASURED * 1e9)
         t_fp4 = tokens_global / world * FLOPS_PER_TOKEN / (4 * peaks["bf16_tflops"] * 1e12)
-        one_gpu = one_gpu_same_workload(chain, flush, tokens_global, zipf, args.steps)
+        one_gpu = one_gpu_same_workload(w_all, flush, tokens_global, zipf, args.steps)
         cfg = workload_config(tokens_global, world)
         cfg.update({"tokens_per_rank": t_loc, "expert_placement": placement, "routing_skew": "zipf 1.1" if zipf else "none",
                     "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
@@ -159,10 +197,11 @@ def run(args):
                              "nvlink_bytes_per_rank_per_direction": link_bytes, "nvlink_gbs_peak": NVLINK_GBS_MEASURED,
                              "traffic": None},
                 "cpu_baseline": None,
+                "parity_checked": parity_ok, "parity_mismatching_elements": parity_bad,
+                "parity_note": "every rank, its own tokens, 2 inputs: bit-for-bit against the single-GPU layer with all 128 experts",
                 "one_gpu_same_workload": one_gpu,
                 "e2e": {"value": tokens_global / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                         "h2d_bytes_per_step": tokens_global * (2 * H + 4 * E), "d2h_bytes_per_step": tokens_global * 2 * H},
                 "gpu_launches": args.steps * 8, "wall_ms_per_step": wall_ms / args.steps, "clocks": clocks.summary()}
-        print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()
+        return line
+    return None

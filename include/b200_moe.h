@@ -117,6 +117,18 @@ int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_
 int b200moe_permute_static(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
                            int32_t* sorted_ids, float* sorted_w, int32_t* block_expert, int32_t* num_valid, void* stream);
 
+/* How long a wait inside a kernel (on an mbarrier, or on the completion count of b200moe_gemm12) may last before the
+ * kernel gives up, sets status = B200MOE_DEV_TIMEOUT, lets its copies land, frees its tensor memory and returns
+ * (the bounded form of the reference's wait_ready, MOE/a16w4_utils.py:44-61, which spins without a limit). Default
+ * 2,000,000,000 ns. Applies to the CURRENT device and to kernels launched after the call; synchronous. */
+int b200moe_set_wait_limit_ns(uint64_t ns);
+
+/* b200moe_route_sort on split-K partials (layout as in b200moe_route_topk), added in split order. */
+int b200moe_route_sort_partials(const float* partials, int64_t stride_t, int64_t stride_s, int splits, const float* bias,
+                                int64_t tokens, int num_experts, int mode, float scale, int bm, float* out_w,
+                                int32_t* out_ids, int32_t* sorted_ids, float* sorted_w, int32_t* block_expert,
+                                int32_t* num_valid, int32_t* scratch, void* stream);
+
 /* Router top-4 on plain fp32 logits [T][num_experts] followed by the routing sort; one single-CTA kernel up to 32
  * tokens, b200moe_route_topk + b200moe_permute above (the fused top-k + sort of the reference's small tier,
  * MOE/router_topk_sorted.py:43). Outputs of both. */
@@ -127,14 +139,14 @@ int b200moe_route_sort(const float* logits, const float* bias, int64_t tokens, i
 /* Gather of quantised token rows into sorted order with the scales laid out as atoms (the activation-scale gather of
  * MOE/common/scale_sort_tile_map.py:253 scale_sort_tile_map, plus the row gather the reference does inside GEMM1,
  * MOE/gemm1_prefill_h6144_i768.py:209-228). xq_sorted [max_rows][3072], sfx [max_rows/bm][48][512]; padding rows are
- * written as zero codes with scale byte 127. by_pair != 0: codes/scales hold one row per (token, slot) pair, row
+ * written as zero codes with scale byte 1 (the byte of an all-zero block). by_pair != 0: codes/scales hold one row per (token, slot) pair, row
  * 4*token+slot (rows that arrived from other ranks), instead of one row per token. */
 int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids,
                           const int32_t* num_valid, int64_t tokens, int bm, int by_pair, int64_t max_rows,
                           uint8_t* xq_sorted, uint8_t* sfx, void* stream);
 
 /* Quantisation fused with the gather: bf16 x [T][6144] -> xq_sorted / sfx as above, same bits as b200moe_quant_mxfp4
- * followed by b200moe_dispatch_rows except that padding rows get the scale byte of an all-zero block (1)
+ * followed by b200moe_dispatch_rows
  * (the fused router + quant launches of the reference, MOE/router_topk_mxfp4_mxfp8_quant.py:35). `done` (may be null):
  * int32 [max_rows/bm], zeroed by this kernel for a following b200moe_gemm12. */
 int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid, int64_t tokens,
@@ -213,6 +225,20 @@ int b200moe_gemm2_simt(const uint8_t* w2, const uint8_t* w2_scale, const uint8_t
  * out = bf16( (((+0 + s0) + s1) + s2) + s3 (+ shared) ) in fp32, bit-exact. shared may be null. */
 int b200moe_reduce_slots(const void* slots_bf16, const void* shared_bf16, int64_t tokens, void* out_bf16, void* stream);
 
+/* The layer's fused tail (amd_kernels/collectives/pull_collectives_ranks4/README.md:25-27
+ * slots4_reduce_scatter_add_rmsnorm_mxfp8 at one rank; sum: .../pull_collectives_ranks4/reference.py:74-91
+ * slots4_reduce_scatter_reference; add + norm + quant: amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py steps 2-4):
+ *   x = bf16((((s0 + s1) + s2) + s3) (+ shared)) in fp32;  s = fp32(x) + fp32(residual);  residual_out = bf16(s);
+ *   y = (s * rstd) * (weight + 1), rstd = 1/sqrt(sum(s^2)/6144 + eps);  out = bf16(y) (out may be null);
+ *   per 32 columns of y: scale byte = clamp(ceil(log2(max(max|y|, 2^-126) / 448)) + 127, 0, 254) and E4M3 codes of
+ *   y * 2^(127 - byte) (codes8 [T][6144] and scales8 [T][192] row-major; both may be null).
+ * The sum and the residual are bit-exact; y is fp32 arithmetic with a fixed-order sum of squares (the same bits on every
+ * run), within the reference's tolerances of its fp64 statement. slots bf16 [T][4][6144], shared (may be null) /
+ * residual / residual_out / out bf16 [T][6144], weight bf16 [6144]; all 16-byte aligned. */
+int b200moe_reduce_slots_add_rmsnorm_quant(const void* slots_bf16, const void* shared_bf16, const void* residual_bf16,
+                                           const void* weight_bf16, float eps, int64_t tokens, void* residual_out_bf16,
+                                           void* out_bf16, uint8_t* codes8, uint8_t* scales8, void* stream);
+
 /* ---- the MXFP8 shared expert (MOE/shared_expert.py: SharedWeights, shared_expert; oracle MOE/reference.py:162-189
  * shared_mxfp8_quant_ref / shared_mxfp8_ref): a dense SwiGLU-OAI MLP on every token, E4M3 codes with one E8M0 scale
  * per 32 elements for weights, the input and the SwiGLU output; fp32 accumulation; bf16 result rows.
@@ -278,10 +304,21 @@ typedef struct b200moe_weights {
   int num_experts;
   int route_mode;
   float route_scale;
+  const float* gate;   /* router weight fp32 [num_experts][6144]; needed by b200moe_forward_x only, else may be null */
 } b200moe_weights;
 size_t b200moe_workspace_bytes(int64_t tokens, int num_experts);
 int b200moe_forward(const b200moe_weights* w, const void* x_bf16, const float* logits, int64_t tokens, void* workspace,
                     size_t workspace_bytes, void* slots_bf16, void* out_bf16, int32_t* status, void* stream);
+
+/* The same layer with the router inside the call -- the call vLLM makes, MOE/chain.py:127-197 mxfp4_moe(x, w) with its
+ * fused router + input quantiser (MOE/chain.py:75-103; MOE/router_mxfp4_quant_line_layout.py:48-400): one pass over x
+ * gives the split-K logit partials (w->gate) and the row-major MXFP4 operands, then top-4 on the partials added in split
+ * order -> sort -> gather of the quantised rows -> GEMM1 -> GEMM2 -> (reduce). Workspace of
+ * b200moe_workspace_bytes_x(T, num_experts) bytes, 256-byte aligned. Same slots / out as b200moe_forward fed with the
+ * logits b200moe_router_gemm produces. */
+size_t b200moe_workspace_bytes_x(int64_t tokens, int num_experts);
+int b200moe_forward_x(const b200moe_weights* w, const void* x_bf16, int64_t tokens, void* workspace,
+                      size_t workspace_bytes, void* slots_bf16, void* out_bf16, int32_t* status, void* stream);
 
 /* Host-buffer form of the same call, the one the end-to-end benchmark times: copies x and logits from (pinned) host
  * memory to `dev_x`/`dev_logits`, runs b200moe_forward, copies out to `host_out`, all on `stream`, no synchronise. */

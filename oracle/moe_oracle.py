@@ -207,6 +207,102 @@ def moe_layer(x_bits, logits, w13, w13_scale, w2, w2_scale, *, mode="softmax", b
     return dict(out=reduce_slots_bf16(slot_bits), slots=slot_bits, ids=ids.astype(np.int32), weights=w32, xq=xq, xs=xs)
 
 
+# ----------------------------------------------------------------------------------------------- fused tail
+# Restates amd_kernels/collectives/pull_collectives_ranks4/reference.py:74-91 (the local slot sum of
+# slots4_reduce_scatter_reference, = amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py slots4_local_reference) and
+# steps 2-4 of amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py (add_rmsnorm_reference, mxfp8_scale_reference,
+# mxfp8_codes); pinned by tests/golden/tail.npz, which those functions wrote.
+TAIL_FP8_MAX, TAIL_TINY = 448.0, 2.0 ** -126
+TAIL_OUT_ULPS, TAIL_OUT_MISMATCH, TAIL_OUT_COS = 1, 1e-3, 0.99999       # the norm reference's tolerances
+TAIL_SCALE_MISMATCH, TAIL_CODE_MISMATCH, TAIL_MXFP8_COS = 1e-3, 1e-3, 0.999
+
+
+def slots4_local(slots_bits: np.ndarray, shared_bits: np.ndarray | None = None) -> np.ndarray:
+    """bf16 bits [M, 4, H] (+ [M, H]) -> bf16 bits [M, H]: (((s0 + s1) + s2) + s3) + shared in float32 starting FROM s0
+    (not from +0: a row of -0.0 stays -0.0), one rounding."""
+    acc = bf16_to_f32(slots_bits[:, 0])
+    for k in range(1, slots_bits.shape[1]):
+        acc = acc + bf16_to_f32(slots_bits[:, k])
+    if shared_bits is not None:
+        acc = acc + bf16_to_f32(shared_bits)
+    return f32_to_bf16(acc)
+
+
+def add_rmsnorm(x_bits: np.ndarray, residual_bits: np.ndarray, weight_bits: np.ndarray, eps: float):
+    """-> (y float64 [M, H], residual out bf16 bits): s = fp32(x) + fp32(residual) (one float32 rounding), residual out =
+    bf16(s), y = s * rsqrt(sum(s^2) / H + fp32(eps)) * (weight + 1) in float64; a sum of squares above the float32
+    maximum counts as +inf."""
+    s = (bf16_to_f32(x_bits) + bf16_to_f32(residual_bits)).astype(np.float32)
+    s64 = s.astype(np.float64)
+    with np.errstate(over="ignore", invalid="ignore"):
+        ss = (s64 * s64).sum(-1, keepdims=True)
+        ss = np.where(ss > np.finfo(np.float32).max, np.inf, ss)
+        y = s64 / np.sqrt(ss / s.shape[-1] + np.float64(np.float32(eps))) * (bf16_to_f32(weight_bits).astype(np.float64) + 1.0)
+    return y, f32_to_bf16(s)
+
+
+def tail_mxfp8_scale(y64: np.ndarray) -> np.ndarray:
+    """[M, H/32] E8M0 bytes: a = max(max|y|, 2^-126) per 32 columns (NaNs skipped), byte = clamp(ceil(log2(fp32(a) / 448))
+    + 127, 0, 254), the division rounded to float32; 254 for an infinite a."""
+    m, h = y64.shape
+    mag = np.abs(y64)
+    mag = np.where(np.isnan(mag), 0.0, mag)
+    with np.errstate(over="ignore"):
+        a = np.maximum(mag.reshape(m, h // 32, 32).max(-1).astype(np.float32), np.float32(TAIL_TINY))
+        d = (a / np.float32(TAIL_FP8_MAX)).astype(np.float32).astype(np.float64)
+    man, ex = np.frexp(np.where(np.isinf(d), 1.0, d))
+    ceil_log2 = ex.astype(np.int64) - (man == 0.5)
+    sb = np.clip(ceil_log2 + 127, 0, 254)
+    return np.where(np.isinf(a), 254, sb).astype(np.uint8)
+
+
+def tail_mxfp8_codes(y64: np.ndarray, scale_bytes: np.ndarray) -> np.ndarray:
+    """[M, H] E4M3 bytes of y at the given scale bytes: y * 2^(127 - byte) rounded to float32, clamped to +-448, round to
+    nearest even (finite inputs)."""
+    m, h = y64.shape
+    q = (y64.reshape(m, h // 32, 32) * np.exp2(127.0 - scale_bytes.astype(np.float64))[:, :, None]).astype(np.float32)
+    return f32_to_e4m3(np.clip(q, -TAIL_FP8_MAX, TAIL_FP8_MAX)).reshape(m, h)
+
+
+def tail_dequant(codes: np.ndarray, scale_bytes: np.ndarray) -> np.ndarray:
+    m, h = codes.shape
+    v = e4m3_to_f32(codes).astype(np.float64).reshape(m, h // 32, 32)
+    return (v * np.exp2(scale_bytes.astype(np.float64) - 127.0)[:, :, None]).reshape(m, h)
+
+
+def bf16_ulp(v: np.ndarray) -> np.ndarray:
+    """The bf16 spacing at |v| (2^-133 at zero and among the subnormals)."""
+    _, e = np.frexp(np.asarray(v, dtype=np.float64))
+    e = np.where(v == 0, -125, e)
+    return np.exp2(np.maximum(e.astype(np.float64) - 8.0, -133.0))
+
+
+def compare_tail(out_bits, codes, scale_bytes, y64) -> dict:
+    """The norm reference's acceptance statistics (its compare_out / compare_mxfp8) of a bf16 ``out`` and row-major
+    MXFP8 ``codes`` / ``scale_bytes`` against the float64 y, finite y assumed. Any of the three may be None."""
+    stats = {}
+    if out_bits is not None:
+        o = bf16_to_f32(out_bits).astype(np.float64)
+        err = np.abs(o - y64)
+        ulp = np.maximum(bf16_ulp(y64), bf16_ulp(o))
+        yb = bf16_to_f32(f32_to_bf16(y64.astype(np.float32))).astype(np.float64)
+        stats.update(bad_ulp=int((err > TAIL_OUT_ULPS * ulp).sum()), mismatch=float((o != yb).mean()),
+                     cos=float((o * y64).sum() / np.linalg.norm(o) / np.linalg.norm(y64)))
+    if codes is not None:
+        ref_sb = tail_mxfp8_scale(y64)
+        sd = np.abs(scale_bytes.astype(np.int64) - ref_sb.astype(np.int64))
+        ref_codes = tail_mxfp8_codes(y64, scale_bytes)
+        diff = codes != ref_codes
+        mag = lambda c: (c & 0x7F).astype(np.int64)  # noqa: E731
+        near = (np.abs(mag(codes) - mag(ref_codes)) <= 1) & (((codes & 0x80) == (ref_codes & 0x80)) | (mag(codes) == 0)
+                                                             | (mag(ref_codes) == 0))
+        deq = tail_dequant(codes, scale_bytes)
+        stats.update(scale_max_diff=int(sd.max()), scale_mismatch=float((sd != 0).mean()),
+                     code_mismatch=float(diff.mean()), code_far=int((diff & ~near).sum()),
+                     mxfp8_cos=float((deq * y64).sum() / np.linalg.norm(deq) / np.linalg.norm(y64)))
+    return stats
+
+
 # ----------------------------------------------------------------------------------------------- shared expert (MXFP8)
 def _e4m3_table() -> np.ndarray:
     """float32 value of every E4M3 (fn) byte; 0x7f / 0xff are NaN."""

@@ -14,6 +14,9 @@ Fixtures (inputs are stored or re-derivable from the stated seed; outputs come f
   moe_small.npz  E=8, H=256, I=64, T=32 MXFP4 layer            -> w4a4_moe_ref
   shared.npz   bf16 rows -> shared_mxfp8_quant_ref; seeded MXFP8 weights -> shared_mxfp8_ref; torch's E4M3 cast
   sidecar.npz  bf16 rows -> both quantisers -> mxfp4_sidecar_pack_ref (mask) and mxfp4_sidecar_unpack_ref (== the FP4 codes)
+  tail.npz     bf16 slots / shared / residual / norm weight -> slots4_local_reference, add_rmsnorm_reference,
+               mxfp8_scale_reference, mxfp8_codes of amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py (the contract of
+               the fused MoE tail, amd_kernels/collectives/pull_collectives_ranks4/reference.py:74-91 for the slot sum)
   moe_config0.npz  the benchmark's configuration 0 (T=16, E=128, H=6144, I=768, seed 0; inputs re-derived from the seed
                by oracle.moe_oracle.make_weights / make_inputs, their CRC32 stored) -> w4a4_moe_ref on softmax top-4
                routing, and on the reference's sigmoid+bias routing
@@ -34,6 +37,14 @@ from oracle import moe_oracle as orc  # noqa: E402
 def load_reference(root):
     path = os.path.join(root, "amd_kernels/moe/mxfp4_h6144_i768_e128_top4/reference.py")
     spec = importlib.util.spec_from_file_location("reference_moe", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_norm_reference(root):
+    path = os.path.join(root, "amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py")
+    spec = importlib.util.spec_from_file_location("reference_norm", path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
@@ -152,6 +163,29 @@ def main():
     assert torch.equal(back, q4)
     np.savez_compressed(os.path.join(HERE, "sidecar.npz"), x_bits=bits(xc), q4=q4.numpy(), s4=s4.numpy(),
                         q8=q8c.view(torch.uint8).numpy(), s8=s8c.numpy(), mask=mask.numpy())
+    # ---- fused tail: slot sum + shared, residual add, Gemma RMSNorm, MXFP8 of the fp32 norm
+    norm = load_norm_reference(root)
+    g = torch.Generator().manual_seed(44)
+    m = 6
+    slots = (torch.randn((m, 4, 6144), generator=g) * torch.exp2(torch.randint(-6, 4, (m, 4, 1), generator=g).float())).bfloat16()
+    shared = torch.randn((m, 6144), generator=g).bfloat16()
+    resid = (torch.randn((m, 6144), generator=g) * 2.0).bfloat16()
+    weight = (torch.randn((6144,), generator=g) * 0.1).bfloat16()
+    slots[0, :, :64] = -0.0   # a run of signed zeros through the whole tail
+    shared[0, :64] = -0.0
+    resid[0, :32] = -0.0
+    resid[1, :64] = -slots[1, :, :64].float().sum(0).bfloat16()   # small sums next to cancellation
+    slots[2] *= 2.0 ** -20    # a quiet row: tiny rms, eps matters
+    shared[2] *= 2.0 ** -20
+    resid[2] *= 2.0 ** -20
+    x = norm.slots4_local_reference(slots, shared)
+    x_noshared = norm.slots4_local_reference(slots, torch.zeros_like(shared))
+    y64, res_out = norm.add_rmsnorm_reference(x, resid, weight, 1e-6)
+    sb = norm.mxfp8_scale_reference(y64)
+    codes = norm.mxfp8_codes(y64, sb)
+    np.savez_compressed(os.path.join(HERE, "tail.npz"), slots=bits(slots), shared=bits(shared), residual=bits(resid),
+                        weight=bits(weight), eps=np.float32(1e-6), x=bits(x), y64=y64.numpy(), residual_out=bits(res_out),
+                        scales=sb.numpy(), codes=codes.numpy(), out=bits(y64.float().bfloat16()))
     print("golden fixtures written to", HERE)
 
 

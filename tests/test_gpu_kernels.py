@@ -152,7 +152,7 @@ def test_dispatch_rows_gathers_codes_and_scale_atoms(C, m, bm):
     got = xq.cpu().numpy()[:nv]
     assert np.array_equal(got[live], codes[tok[live]]) and not got[~live].any()
     sc = atoms_to_rowmajor(sfx.cpu().numpy(), bm)[:nv]
-    assert np.array_equal(sc[live], scales[tok[live]]) and np.all(sc[~live] == 127)
+    assert np.array_equal(sc[live], scales[tok[live]]) and np.all(sc[~live] == 1)
 
 
 def test_reduce_golden_and_shared(C):

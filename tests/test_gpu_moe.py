@@ -53,8 +53,10 @@ def run_stages(C, w, xq, ids, wts, bm, tc=True, rows=None):
 @pytest.mark.parametrize("tokens,bm", [(1, 16), (16, 16), (40, 32), (100, 64), (200, 128), (300, 16)])
 @pytest.mark.parametrize("kind", ["uniform", "one", "dup"])
 def test_tensor_core_gemms_equal_cuda_core_gemms(C, tokens, bm, kind):
-    """4 experts, every block height: h codes and scales and the bf16 slots equal the CUDA-core kernels bit for bit
-    (both accumulate exact products in fp32; codes could differ only at rounding ties, which these seeds do not hit)."""
+    """4 experts, every block height, against the CUDA-core kernels. Both accumulate exact products in fp32 but in a
+    different order, so an h value that lands next to a rounding boundary may take the neighbouring code: fewer than
+    1e-4 of the h codes and scale bytes may differ; where none differs the bf16 slots are equal bit for bit, and the
+    slot sums always meet the oracle tolerances."""
     (w13, s13, w2, s2), gen = orc.make_weights(seed=tokens, experts=4)
     xb, _ = orc.make_inputs(gen, tokens, experts=4)
     w = C.MoeWeights.from_row_major(None, None, dev(w13), dev(s13), dev(w2), dev(s2), keep_row_major=True)
@@ -118,6 +120,53 @@ def test_reference_routing_rule_and_distributions(C):
     xq, xs = orc.quant_mxfp4(x.float().numpy())
     ref = orc.w4a4_moe(xq, xs, w13, s13, w2, s2, wt.cpu().numpy(), ids.cpu().numpy())
     check_against_oracle(out.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("mode", ["sigmoid_bias", "softmax"])
+@pytest.mark.parametrize("tokens", [1, 5, 32, 33, 256, 2048])
+def test_entry_with_the_router_inside(C, layer, tokens, mode):
+    """``mxfp4_moe(x, w)`` WITHOUT ``router_logits`` -- the call a server makes (reference chain.py:127-197; its test
+    tests/moe/.../test_entry.py:94-104): the router GEMM fused with the input quantiser, top-4, sort, gather, GEMMs and
+    reduce in one C-ABI call (b200moe_forward_x). Routing ids against the fp64 logits on decided rows (reference.py:127-148),
+    weights to 1e-3; the slots bit for bit against the staged kernels on the same routing; sampled tokens against the CPU
+    oracle; graph replay into poisoned buffers."""
+    raw, w0, _, _ = layer
+    sigmoid = mode == "sigmoid_bias"
+    gen = torch.Generator().manual_seed(7000 + tokens)
+    x = torch.randn((tokens, H), generator=gen).bfloat16()
+    gate = torch.randn((128, H), generator=gen) / H ** 0.5
+    bias = torch.randn((128,), generator=gen) * 0.01 if sigmoid else None
+    scale = 2.0 if sigmoid else 1.0
+    w = C.MoeWeights(gate.cuda(), None if bias is None else bias.cuda(), w0.w13, None, w0.w2, None, scale, mode)
+    xd = x.cuda()
+    out = C.mxfp4_moe(xd, w)
+    slots, shared = C.mxfp4_moe(xd, w, return_partials=True)
+    wt, ids = C.route(xd, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0 and shared is None
+    logits64 = (x.double() @ gate.double().t()).numpy()
+    if sigmoid:
+        wr, ir, vals = orc.route_sigmoid_bias(logits64, bias.numpy(), scale)
+    else:
+        wr, ir, vals = orc.route_softmax(logits64, scale)
+    dec = orc.decided(vals, eps=5e-4)  # the router's partials are within 2^-18 * sum|x||w| ~ 1.5e-4 of the fp64 logits
+    assert dec.mean() > 0.9
+    assert np.array_equal(ids.cpu().numpy()[dec], ir[dec])
+    np.testing.assert_allclose(wt.cpu().numpy()[dec.all(1)], wr[dec.all(1)], atol=1e-3, rtol=0)
+    staged = C.mxfp4_moe_experts(C.mxfp4_quant(xd), wt, ids, w)
+    assert torch.equal(slots, staged), "the one-call entry and the staged kernels disagree"
+    assert np.array_equal(bits_of(out), orc.reduce_slots_bf16(bits_of(slots)))
+    pick = np.unique(np.linspace(0, tokens - 1, 6).astype(int))
+    xq, xs = orc.quant_mxfp4(x.float().numpy())
+    ref = oracle_slots(xq, xs, raw, ids.cpu().numpy(), wt.cpu().numpy(), tokens=pick)
+    check_against_oracle(slots.float().cpu().numpy()[pick].sum(1), ref.sum(1))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        replayed = C.mxfp4_moe(xd, w)
+    replayed.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(replayed, out) and C.last_status() == 0
 
 
 @pytest.mark.parametrize("tokens", [1, 2, 4, 8, 16, 32, 64, 128, 256])

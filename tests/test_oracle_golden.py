@@ -134,3 +134,22 @@ def test_sidecar_pack_and_unpack_match_reference():
     assert mask.shape == (x.shape[0], 768) and (mask == g["mask"]).all()
     assert mask.any()
     assert (orc.sidecar_unpack(mask, s4, q8, s8) == q4).all()
+
+
+def test_fused_tail_matches_reference():
+    """Slot sum + shared, residual add, Gemma RMSNorm and the MXFP8 of the fp32 norm against the reference's
+    slots4_local_reference / add_rmsnorm_reference / mxfp8_scale_reference / mxfp8_codes
+    (amd_kernels/norm/gemma_add_rmsnorm_h6144/reference.py): the sum, residual, scale bytes and codes bit for bit, y to
+    fp64 round-off."""
+    g = golden("tail.npz")
+    x = orc.slots4_local(g["slots"], g["shared"])
+    assert np.array_equal(x, g["x"])
+    y, res = orc.add_rmsnorm(x, g["residual"], g["weight"], float(g["eps"]))
+    assert np.array_equal(res, g["residual_out"])
+    np.testing.assert_allclose(y, g["y64"], rtol=1e-14, atol=0)
+    assert np.array_equal(orc.tail_mxfp8_scale(g["y64"]), g["scales"])
+    assert np.array_equal(orc.tail_mxfp8_codes(g["y64"], g["scales"]), g["codes"])
+    st = orc.compare_tail(g["out"], g["codes"], g["scales"], g["y64"])
+    assert st["bad_ulp"] == 0 and st["code_mismatch"] == 0 and st["scale_mismatch"] == 0
+    # -0.0 runs survive the slot sum (it starts from s0, not from +0) but not the library's plain slot reduce
+    assert (x[0, :64] == 0x8000).all() and (orc.reduce_slots_bf16(g["slots"])[0, :64] == 0).all()
