@@ -1,0 +1,469 @@
+// Prefill GEMM1 (+ SwiGLU-OAI + MXFP4 requantisation) on CTA PAIRS: a cluster of two CTAs on neighbouring SMs runs one
+// tcgen05.mma.cta_group::2 of M = 256 token rows x N = 256 weight rows x K = 64 per instruction.
+//
+// Why pairs. With one CTA per tile (128 x 128 per MMA) every 64 cycles of tensor math read 8 KB of operands from shared
+// memory, and the same bytes were written there by the copy engine just before: shared memory moves 128 bytes per cycle
+// and is the limit (tensor pipe measured 50 % busy). In a pair each CTA holds its own 128 token rows (its half of A) and
+// 128 of the 256 weight rows (its half of B); the hardware hands each B half to the partner, so per 512 cycles of math a
+// CTA writes 34 KB and reads 32 KB instead of 68 + 64.
+//
+// Work. The routing sort (block height 128) lays an expert's row blocks next to one another. A unit is (two consecutive
+// blocks of one expert, or its last odd block alone) x (a pair of W13 tiles = 128 intermediate columns, gate and up). CTA
+// r of the pair loads the tokens of block b0 + r and weight tile 2*tp + r; both load the 1 KB of scales of both tiles.
+// With a single block the second CTA still supplies its weight half but has no rows of its own.
+//
+//   warp 0     producer (both CTAs): TMA tile loads, all completing on the LEADER's (CTA 0) full barrier
+//   warp 1     allocates / frees tensor memory (both CTAs); in the leader one thread issues the MMAs for both
+//   warps 2, 11 leader: one thread each copies half of the stage's scales into tensor memory in both CTAs
+//              (tcgen05.cp.cta_group::2); two threads because every tcgen05 instruction costs its thread ~60 cycles
+//   warps 3-10 epilogue (both CTAs): thread = one token row (TMEM lane), everything in registers; the accumulator is
+//              handed back as soon as it sits in registers, so the next unit's MMAs run under the epilogue's arithmetic
+//
+// No load is a multicast load; stage release and accumulator hand-over use one plain tcgen05.commit per CTA. Every wait
+// is bounded as in the other kernels (status word B200MOE_DEV_TIMEOUT, drain, free, return).
+#include <cuda.h>
+
+#include "tc_host.cuh"
+#include "tc_ptx.cuh"
+
+namespace b200moe {
+
+struct PairCfg {
+  static constexpr int kStages = 6;
+  static constexpr int kTokOff = 0;                 // this CTA's 128 token rows x 128 bytes (128-byte swizzle)
+  static constexpr int kWOff = 128 * 128;           // this CTA's 128 weight rows x 128 bytes (tile record image)
+  static constexpr int kSfTokOff = 2 * 128 * 128;   // token scales: two atoms
+  static constexpr int kSfWLoOff = kSfTokOff + 2 * kAtomBytes;   // scales of tile 2*tp (weight rows 0..127 of N)
+  static constexpr int kSfWHiOff = kSfWLoOff + 2 * kAtomBytes;   // scales of tile 2*tp+1 (rows 128..255)
+  static constexpr int kStageBytes = kSfWHiOff + 2 * kAtomBytes; // 35840
+  static constexpr int kThreads = 32 * 12;
+  static constexpr int kAccCols = 256;
+  static constexpr int kSfSets = 8;                 // >= kStages; a set: 8 token-scale columns + 16 weight-scale columns
+  static constexpr int kSfCol = kAccCols;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kMaxBlocks = 2880;           // row blocks of 128 at the largest token count the library accepts
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTilePairs = kW13Tiles / 2;
+  static constexpr uint32_t kWeightTx = 128 * 128 + 4 * kAtomBytes;   // per CTA: codes + both tiles' scales
+  static constexpr uint32_t kTokenTx = 128 * 128 + 2 * kAtomBytes;    // per CTA that has a row block
+};
+static_assert(PairCfg::kSfCol + 24 * PairCfg::kSfSets <= PairCfg::kTmemCols, "tensor memory columns");
+static_assert(kW13Tiles % 2 == 0, "W13 tiles come in pairs");
+
+// ------------------------------------------------------------------------------------------------ PTX, pair forms
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load whose bytes are counted on a barrier that may sit in the partner CTA (`bar` is a shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+          "r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_cp_scales_pair(uint32_t taddr, uint32_t desc_lo) {
+  asm volatile("{\n.reg .b64 d;\nmov.b64 d, {%1, %2};\ntcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n}\n" ::"r"(taddr),
+               "r"(desc_lo), "n"(kScaleDescHi)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf4_pair(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
+                                                 uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %7};\nmov.b64 db, {%2, %7};\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate), "n"(kOperandDescHi)
+      : "memory");
+}
+__device__ __forceinline__ void drain_tcgen05_pair(uint32_t bar) {
+  tc_commit_pair(bar);
+  const uint64_t t0 = global_timer(), limit = wait_limit_ns();
+  while (!mbar_try_wait(bar, 0) && global_timer() - t0 < limit) {}
+}
+
+// what a row block is to the pair schedule
+enum : uint8_t { kBlockSkip = 0, kBlockSingle = 1, kBlockPair = 2 };
+
+// ------------------------------------------------------------------------------------------------ kernel
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1)
+    gemm1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_sfx,
+                      const __grid_constant__ CUtensorMap map_wc, const __grid_constant__ CUtensorMap map_ws,
+                      const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid,
+                      uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh, int32_t* status, int num_experts,
+                      int max_blocks) {
+  using C = PairCfg;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[C::kStages];   // used in the leader: both CTAs' bytes of the stage have landed
+  __shared__ __align__(8) uint64_t bar_empty[C::kStages];  // in each CTA: the MMAs that read the stage have completed
+  __shared__ __align__(8) uint64_t bar_sf[C::kStages];     // leader: the stage's scales are in tensor memory
+  __shared__ __align__(8) uint64_t bar_tfull;              // in each CTA: the unit's accumulator is complete
+  __shared__ __align__(8) uint64_t bar_tempty;             // leader: both CTAs' epilogues have read the accumulator
+  __shared__ __align__(8) uint64_t bar_drain[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ uint8_t s_kind[C::kMaxBlocks];
+  __shared__ uint16_t s_unit[C::kMaxBlocks];  // the blocks that start a unit, in order: block | pair << 15
+  __shared__ int s_count[C::kThreads + 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abort_v = &abort_flag;
+  pdl_launch_dependents();
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf[s]), 2);  // the two scale-copy threads
+    }
+    mbar_init(smem_u32(&bar_tfull), 1);
+    mbar_init(smem_u32(&bar_tempty), 16);  // one arrival per epilogue warp of both CTAs
+    mbar_init(smem_u32(&bar_drain[0]), 1);
+    mbar_init(smem_u32(&bar_drain[1]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  pdl_wait();
+  launder(block_expert);
+  launder(num_valid);
+  int n_blocks = __ldcg(num_valid) / 128;
+  if (n_blocks < 0 || n_blocks > max_blocks || n_blocks > C::kMaxBlocks) {
+    if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
+    n_blocks = 0;
+  }
+  // Pair schedule: a block at an even position inside its expert starts a unit (with its successor when that belongs to
+  // the same expert); a block at an odd position is covered by its predecessor's unit.
+  for (int b = threadIdx.x; b < n_blocks; b += C::kThreads) {
+    const int e = __ldcg(block_expert + b);
+    int pos = 0;
+    while (b - 1 - pos >= 0 && __ldcg(block_expert + b - 1 - pos) == e) ++pos;
+    uint8_t kind = kBlockSkip;
+    if ((pos & 1) == 0) kind = (b + 1 < n_blocks && __ldcg(block_expert + b + 1) == e) ? kBlockPair : kBlockSingle;
+    if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
+      atomicExch(status, B200MOE_DEV_BAD_INDEX);
+      kind = kBlockSkip;
+    }
+    s_kind[b] = kind;
+  }
+  __syncthreads();
+  // The units in order, so that they can be dealt evenly: every thread counts the unit-starting blocks of its contiguous
+  // chunk, one thread turns the counts into offsets, every thread writes its chunk's entries.
+  {
+    const int chunk = (n_blocks + C::kThreads - 1) / C::kThreads;
+    const int lo = min(n_blocks, static_cast<int>(threadIdx.x) * chunk), hi = min(n_blocks, lo + chunk);
+    int cnt = 0;
+    for (int b = lo; b < hi; ++b) cnt += s_kind[b] != kBlockSkip;
+    s_count[threadIdx.x] = cnt;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int i = 0; i < C::kThreads; ++i) {
+        const int c = s_count[i];
+        s_count[i] = run;
+        run += c;
+      }
+      s_count[C::kThreads] = run;
+    }
+    __syncthreads();
+    int pos = s_count[threadIdx.x];
+    for (int b = lo; b < hi; ++b)
+      if (s_kind[b] != kBlockSkip) s_unit[pos++] = static_cast<uint16_t>(b | (s_kind[b] == kBlockPair ? 0x8000 : 0));
+  }
+  __syncthreads();
+  const int n_clusters = static_cast<int>(gridDim.x >> 1), cluster = static_cast<int>(blockIdx.x >> 1);
+  const int total = s_count[C::kThreads] * C::kTilePairs;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer (both CTAs)
+    if (lane == 0) {
+      const uint32_t full0 = map_to_cta(smem_u32(&bar_full[0]), 0);  // the leader's barriers, as seen from this CTA
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = cluster; u < total && ok; u += n_clusters) {
+        const uint32_t ub = s_unit[u / C::kTilePairs];
+        const int b0 = static_cast<int>(ub & 0x7fffu), tp = u % C::kTilePairs;
+        const bool pair = (ub & 0x8000u) != 0;
+        const bool have_rows = leader || pair;
+        const int e = __ldcg(block_expert + b0);
+        const int my_block = b0 + static_cast<int>(rank);
+        // rows of the weight matrix seen as [records * 136][128 bytes]: 128 rows of codes, then 8 rows of scales
+        const int rec_mine = ((e * kW13Tiles + 2 * tp + static_cast<int>(rank)) * kK1Tiles) * 136;
+        const int rec_lo = ((e * kW13Tiles + 2 * tp) * kK1Tiles) * 136, rec_hi = rec_lo + kK1Tiles * 136;
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
+          const uint32_t full = full0 + 8u * s, base = tiles + s * C::kStageBytes;
+          if (leader)
+            mbar_arrive_expect_tx(smem_u32(&bar_full[s]),
+                                  2u * C::kWeightTx + (pair ? 2u : 1u) * C::kTokenTx);
+          tma_load_2d_pair(base + C::kWOff, &map_wc, 0, rec_mine + kt * 136, full);
+          tma_load_2d_pair(base + C::kSfWLoOff, &map_ws, 0, rec_lo + kt * 136 + 128, full);
+          tma_load_2d_pair(base + C::kSfWHiOff, &map_ws, 0, rec_hi + kt * 136 + 128, full);
+          if (have_rows) {
+            tma_load_2d_pair(base + C::kTokOff, &map_x, kt * 128, my_block * 128, full);
+            tma_load_2d_pair(base + C::kSfTokOff, &map_sfx, 0, (my_block * (kH / 128) + 2 * kt) * 4, full);
+          }
+        }
+      }
+      if (!ok && leader) drain_copies(bar_full, it, C::kStages);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue (leader only)
+    if (lane == 0 && leader) {
+      // E2M1 x E2M1, UE8M0 scales, M = 256 (128 token rows per CTA), N = 256 weight rows
+      constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (1u << 23) |
+                                  (static_cast<uint32_t>(256 >> 4) << 24);
+      constexpr uint32_t kId0 = kIdesc, kId1 = kIdesc | (2u << 29) | (2u << 4);
+      const uint32_t empty_peer0 = map_to_cta(smem_u32(&bar_empty[0]), 1), tfull_peer = map_to_cta(smem_u32(&bar_tfull), 1);
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int u = cluster; u < total && ok; u += n_clusters) {
+        if (!mbar_wait(smem_u32(&bar_tempty), (ui & 1u) ^ 1u, abort_v, status)) break;
+        tc_fence_after();
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
+          if (!mbar_wait(smem_u32(&bar_sf[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
+          const uint32_t x_lo = lo + (C::kTokOff >> 4), w_lo = lo + (C::kWOff >> 4);
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          // 64 K-elements = 32 bytes per MMA; scale bytes {0,1} or {2,3} of the K-atom's cells
+          tc_mma_mxf4_pair(tmem_base, x_lo, w_lo, kId0, t_sft, t_sfw, static_cast<uint32_t>(kt != 0));
+          tc_mma_mxf4_pair(tmem_base, x_lo + 2, w_lo + 2, kId1, t_sft, t_sfw, 1u);
+          tc_mma_mxf4_pair(tmem_base, x_lo + 4, w_lo + 4, kId0, t_sft + 4, t_sfw + 8, 1u);
+          tc_mma_mxf4_pair(tmem_base, x_lo + 6, w_lo + 6, kId1, t_sft + 4, t_sfw + 8, 1u);
+          tc_commit_pair(smem_u32(&bar_empty[s]));  // the stage is free again, in this CTA ...
+          tc_commit_pair(empty_peer0 + 8u * s);     // ... and in the partner
+        }
+        if (ok) {
+          tc_commit_pair(smem_u32(&bar_tfull));
+          tc_commit_pair(tfull_peer);
+        }
+        ++ui;
+      }
+      if (*abort_v) drain_tcgen05_pair(smem_u32(&bar_drain[0]));
+    }
+  } else if (warp == 2 || warp == 11) {
+    // ---------------------------------------------------------------- scale copies into both CTAs' tensor memory (leader)
+    // warp 2: the token scales and the first K-atom's weight scales of rows 0..127; warp 11: the other three atoms
+    if (lane == 0 && leader) {
+      const bool first = warp == 2;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = cluster; u < total && ok; u += n_clusters) {
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          // token scales: K-atom 0, K-atom 1 (each CTA its own rows); weight scales per K-atom: rows 0..127, rows 128..255
+          if (first) {
+            tc_cp_scales_pair(t_sft, lo + (C::kSfTokOff >> 4));
+            tc_cp_scales_pair(t_sft + 4, lo + ((C::kSfTokOff + kAtomBytes) >> 4));
+            tc_cp_scales_pair(t_sfw, lo + (C::kSfWLoOff >> 4));
+          } else {
+            tc_cp_scales_pair(t_sfw + 4, lo + (C::kSfWHiOff >> 4));
+            tc_cp_scales_pair(t_sfw + 8, lo + ((C::kSfWLoOff + kAtomBytes) >> 4));
+            tc_cp_scales_pair(t_sfw + 12, lo + ((C::kSfWHiOff + kAtomBytes) >> 4));
+          }
+          tc_commit_pair(smem_u32(&bar_sf[s]));
+        }
+      }
+      if (*abort_v) drain_tcgen05_pair(smem_u32(&bar_drain[1]));
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs, warps 3..10)
+    const int q = warp & 3;                 // the TMEM lane quarter this warp may read
+    const int half = ((warp - 3) >> 2) & 1; // which 128 of the 256 accumulator columns (= which W13 tile of the pair)
+    const int tr = q * 32 + lane;           // token row inside the block = TMEM lane
+    const uint32_t tempty_leader = map_to_cta(smem_u32(&bar_tempty), 0);
+    uint32_t ui = 0;
+    for (int u = cluster; u < total; u += n_clusters) {
+      const uint32_t ub = s_unit[u / C::kTilePairs];
+      const int b0 = static_cast<int>(ub & 0x7fffu), tp = u % C::kTilePairs;
+      const bool have_rows = leader || (ub & 0x8000u) != 0;
+      const int b = b0 + static_cast<int>(rank);
+      const int64_t row = static_cast<int64_t>(b) * 128 + tr;
+      // the warp decides together: tcgen05.ld below needs all 32 lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull), ui & 1u, abort_v, status))) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + 128u * half + (static_cast<uint32_t>(q * 32) << 16);
+      // columns of a tile: [gate 32 | up 32 | gate 32 | up 32] of 64 intermediate columns. All 128 values of this thread
+      // go to registers first, then the accumulator is handed back (one arrival per warp, on the leader's barrier): the
+      // next unit's MMAs run while SwiGLU, the block maxima and the codes are computed, all thread-local.
+      uint32_t acc[4][32];
+      if (have_rows) {
+        tc_ld32_nowait(t_acc, acc[0]);
+        tc_ld32_nowait(t_acc + 32, acc[1]);
+        tc_ld32_nowait(t_acc + 64, acc[2]);
+        tc_ld32_nowait(t_acc + 96, acc[3]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader);
+      ++ui;
+      if (!have_rows) continue;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        float h[32];
+        float amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          h[k] = swiglu_oai(__uint_as_float(acc[2 * g][k]), __uint_as_float(acc[2 * g + 1][k]));
+          amax = fmaxf(amax, fabsf(h[k]));
+        }
+        const int sc = quark_even_e8m0(amax);
+        const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
+        uint32_t words[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          uint32_t acc_w = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
+          words[wd] = acc_w;
+        }
+        const int grp = 4 * tp + 2 * half + g;  // 32-column group of the intermediate, 0..23
+        *reinterpret_cast<uint4*>(hq + row * (kI / 2) + grp * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(tr, grp & 3)] =
+            static_cast<uint8_t>(sc);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or leaves while the partner may still signal or read it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+// byte matrix [rows][128], boxes of 128 bytes x box_rows, no swizzle (the bytes are stored as shared memory wants them)
+static int make_flat_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200MOE_E_DRIVER;
+  const cuuint64_t dims[2] = {128, rows};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
+}
+
+// CTA pairs that can be resident at once on the current device (0: cluster launch unavailable)
+static int resident_pairs() {
+  static std::mutex mu;
+  static int pairs[kMaxDevices] = {};
+  static bool known[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[dev]) {
+    int n = 0;
+    if (cudaFuncSetAttribute(gemm1_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes) ==
+        cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * sm_count());
+      cfg.blockDim = dim3(PairCfg::kThreads);
+      cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm1_pair_kernel, &cfg) != cudaSuccess) n = 0;
+    }
+    (void)cudaGetLastError();
+    pairs[dev] = n;
+    known[dev] = true;
+  }
+  return pairs[dev];
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_gemm1_pair_supported(void) { return b200moe::resident_pairs() > 0 ? 1 : 0; }
+
+extern "C" int b200moe_gemm1_swiglu_quant_pair(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted,
+                                               const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
+                                               int64_t max_rows, uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
+  using namespace b200moe;
+  if (!w13t || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status) return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || max_rows % 128 || max_rows / 128 > PairCfg::kMaxBlocks)
+    return B200MOE_E_ARG;
+  if (misaligned(w13t, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) || misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  const int pairs = resident_pairs();
+  if (pairs <= 0) return B200MOE_E_DRIVER;
+  CUtensorMap mx, msf, mwc, mws;
+  int r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), 128);
+  if (r) return r;
+  const uint64_t sf_rows = static_cast<uint64_t>(max_rows / 128) * (kH / 128) * 4;
+  if ((r = make_flat_map(&msf, sfx, sf_rows, 8))) return r;
+  const uint64_t w_rows = static_cast<uint64_t>(num_experts) * kW13Tiles * kK1Tiles * 136;
+  if ((r = make_flat_map(&mwc, w13t, w_rows, 128))) return r;
+  if ((r = make_flat_map(&mws, w13t, w_rows, 8))) return r;
+  const int64_t max_units = max_rows / 128 * PairCfg::kTilePairs;
+  const int clusters = static_cast<int>(max_units < pairs ? max_units : pairs);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(PairCfg::kThreads);
+  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm1_pair_kernel, mx, msf, mwc, mws, block_expert, num_valid, hq, sfh,
+                                           status, num_experts, static_cast<int>(max_rows / 128));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}

@@ -261,7 +261,8 @@ def route_sort(logits: torch.Tensor, w: "MoeWeights", bm: int | None = None):
 
 def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_next: bool = False):
     """GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 -> (h codes [rows, 384], h scale atoms [rows/bm, 6, 512]).
-    ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first."""
+    ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first. (From about 13000 tokens' worth of rows
+    the library runs the CTA-pair kernel of ``grouped_gemm1_pair``; same bits.)"""
     dev = xq_sorted.device
     hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
@@ -270,6 +271,21 @@ def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_nex
                                                       sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
                                                       _ptr(w.w2) if prefetch_next else None,
                                                       _ptr(status_word(dev)), _stream(dev)), "gemm1_swiglu_quant")
+    return hq, sfh
+
+
+def grouped_gemm1_pair(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
+    """``grouped_gemm1`` at block height 128 on CTA pairs (``tcgen05.mma.cta_group::2``, 256 token rows x 256 weight rows
+    per instruction): the same h codes and scale atoms."""
+    if sort.bm != 128:
+        raise ValueError("the CTA-pair GEMM1 serves block height 128")
+    dev = xq_sorted.device
+    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant_pair(_ptr(w.w13), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
+                                                           _ptr(sort.block_expert), _ptr(sort.num_valid), sort.max_rows,
+                                                           _ptr(hq), _ptr(sfh), _ptr(status_word(dev)), _stream(dev)),
+               "gemm1_swiglu_quant_pair")
     return hq, sfh
 
 
@@ -496,7 +512,7 @@ def set_wait_limit_ns(ns: int) -> None:
     _lib.check(_lib.load().b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
 
 
-WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000)  # one-launch GEMMs, one size per block height, the two-CTA GEMM1
+WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000, 14000)  # one-launch GEMMs, one size per block height, the two-CTA and the CTA-pair GEMM1
 
 
 def warm_up_mxfp4_moe(w, *, partials=False, workers=None):

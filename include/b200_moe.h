@@ -175,6 +175,16 @@ int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8
                                const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, int bm,
                                uint8_t* hq, uint8_t* sfh, const uint8_t* prefetch_w2t, int32_t* status, void* stream);
 
+/* The same GEMM1 at block height 128 on CTA pairs: a cluster of two CTAs issues tcgen05.mma.cta_group::2 of 256 token rows
+ * (two row blocks of one expert) x 256 weight rows (two W13 tiles), each CTA staging its own half of both operands, so
+ * shared memory moves half the bytes per flop (the role of the reference's persistent prefill kernel at its widest tile,
+ * MOE/gemm1_prefill_h6144_i768.py:560-598 K-loop, :689-768 epilogue). Same inputs, outputs and bits as
+ * b200moe_gemm1_swiglu_quant with bm = 128. b200moe_gemm1_pair_supported(): 1 when the current device can launch it. */
+int b200moe_gemm1_pair_supported(void);
+int b200moe_gemm1_swiglu_quant_pair(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
+                                    const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,
+                                    uint8_t* sfh, int32_t* status, void* stream);
+
 /* Grouped GEMM2, times the routing weight, rounded to bf16, one writer per (token, slot, column)
  * (MOE/gemm2_a4w4_small.py:19-79, MOE/gemm2_a4w4_bm128.py:52; oracle MOE/reference.py:73-74).
  * slots bf16 [T][4][6144]; padding rows are dropped. */

@@ -77,6 +77,32 @@ def test_tensor_core_gemms_equal_cuda_core_gemms(C, tokens, bm, kind):
     check_against_oracle(slots.float().cpu().numpy().sum(1), slots_r.float().cpu().numpy().sum(1))
 
 
+@pytest.mark.parametrize("tokens,kind", [(300, "uniform"), (2048, "uniform"), (3000, "hot"), (700, "one"), (5, "dup")])
+def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
+    """GEMM1 on CTA pairs (tcgen05.mma.cta_group::2, two row blocks of an expert x two W13 tiles per unit, odd last blocks
+    alone) writes the h codes and scales of the one-CTA kernel bit for bit: experts with one, an even and an odd number of
+    128-row blocks, and one expert holding every row."""
+    from amd_kernels_b200 import _lib
+    if not _lib.load().b200moe_gemm1_pair_supported():
+        pytest.skip("the device cannot launch CTA pairs")
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(31 + tokens)
+    xb, _ = orc.make_inputs(gen, tokens)
+    ids, wts = make_routing(tokens, kind, seed=tokens)
+    sb = C.moe_sort(dev(ids), dev(wts), 128, w.num_experts)
+    xq, sfx = C.quant_dispatch(bf16_dev(xb), sb)
+    a_h, a_s = C.grouped_gemm1(xq, sfx, sb, w)
+    b_h, b_s = C.grouped_gemm1_pair(xq, sfx, sb, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    nv = int(sb.num_valid[0])
+    live = ((sb.sorted_ids[:nv] & 0xFFFFFF) < tokens)
+    assert torch.equal(a_h[:nv][live], b_h[:nv][live])
+    sa, sp = (atoms_to_rowmajor(t.cpu().numpy(), 128)[:nv][live.cpu().numpy()] for t in (a_s, b_s))
+    assert np.array_equal(sa, sp)
+    assert torch.equal(b_h, C.grouped_gemm1_pair(xq, sfx, sb, w)[0])
+
+
 def test_config0_against_reference_golden(C, layer):
     """Configuration 0 (T=16) end to end against the output of the reference's own w4a4_moe_ref."""
     raw, w, xb, lg = layer
