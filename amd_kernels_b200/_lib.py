@@ -17,7 +17,8 @@ ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
 class Weights(Structure):
     """struct b200moe_weights"""
     _fields_ = [("w13t", c_void_p), ("w2t", c_void_p), ("bias", c_void_p),
-                ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float), ("gate", c_void_p)]
+                ("num_experts", c_int), ("route_mode", c_int), ("route_scale", c_float), ("gate", c_void_p),
+                ("gate_split", c_void_p)]
 
 
 _P = c_void_p
@@ -30,6 +31,8 @@ SIGNATURES = {
     "b200moe_preshuffle_w2": (c_int, [_P, _P, c_int, _P, _P]),
     "b200moe_router_splits": (c_int, [c_int64]),
     "b200moe_router_gemm": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P]),
+    "b200moe_router_split_gate": (c_int, [_P, c_int, _P, _P]),
+    "b200moe_router_gemm_tc": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P]),
     "b200moe_route_topk": (c_int, [_P, c_int64, c_int64, c_int, _P, c_int64, c_int, c_int, c_float, _P, _P, _P]),
     "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["abi.cu", "route_sort.cu", "router_gemm.cu", "quant.cu", "preshuffle.cu", "reduce.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "shared_tc.cu", "sidecar.cu", "tail.cu"]
+SOURCES = ["abi.cu", "route_sort.cu", "router_gemm.cu", "router_tc.cu", "quant.cu", "preshuffle.cu", "reduce.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "shared_tc.cu", "sidecar.cu", "tail.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]
 

@@ -423,6 +423,8 @@ static int resident_pairs() {
   return pairs[dev];
 }
 
+int set_wait_limit_pair(unsigned long long ns) { return set_wait_limit_here(ns); }
+
 }  // namespace b200moe
 
 extern "C" int b200moe_gemm1_pair_supported(void) { return b200moe::resident_pairs() > 0 ? 1 : 0; }

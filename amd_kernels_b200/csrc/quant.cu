@@ -33,6 +33,50 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const uint4* __restric
   (void)k;
 }
 
+// Row-major quantisation at prefill sizes: one 256-thread CTA per token row, its three 16-byte loads per thread in flight
+// at once; codes [T][3072] and scales [T][192], the bits of quant_mxfp4_kernel. Used ahead of the gather so that a token is
+// read and quantised once, not once per routed slot.
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint4* __restrict__ x, uint8_t* __restrict__ codes,
+                                                         uint8_t* __restrict__ scales) {
+  pdl_enter(x);
+  constexpr int kIters = kH / 8 / 256;  // 3
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x;
+  const uint4* src = x + row * (kH / 8);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(codes + row * (kH / 2));
+  uint8_t* sdst = scales + row * (kH / 32);
+  uint4 raw[kIters];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) raw[it] = __ldcs(src + it * 256 + threadIdx.x);
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const uint32_t rr[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(rr[j] << 16);
+      v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const int e = quark_even_e8m0(amax);
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);  // 2^(127-e), exact
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
+    dst[idx] = packed;
+    // 4 lanes share a 32-element block; lanes 0 and 16 gather four neighbouring blocks' bytes into one 4-byte store
+    uint32_t sc = static_cast<uint32_t>(e);
+    sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
+    sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
+    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * 4) = sc;
+  }
+}
+
 // One warp per sorted row: copies the token's 3072 code bytes and scatters its 192 scale bytes into the block's atoms.
 // Also zeroes `done` (may be null), the per-block completion counts of a following one-launch GEMM1+GEMM2.
 __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __restrict__ codes,
@@ -213,6 +257,10 @@ __global__ void __launch_bounds__(256) quant_push_kernel(const uint4* __restrict
 
 }  // namespace b200moe
 
+namespace b200moe {
+int quant_rows(const void* x_bf16, int64_t tokens, uint8_t* codes, uint8_t* scales, void* stream);
+}
+
 extern "C" int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const int32_t* send_ids, const float* send_w,
                                   const int32_t* send_rank, int64_t tokens, int world, int rank, int experts_per_rank,
                                   int interleaved, void* const* peer_codes, void* const* peer_scales,
@@ -255,6 +303,7 @@ extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, ui
   if (!x_bf16 || !codes || !scales || tokens < 0 || k <= 0 || (k % 256) != 0) return B200MOE_E_ARG;
   if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(codes) & 3)) return B200MOE_E_ALIGN;
   if (tokens == 0) return 0;
+  if (k == kH && tokens >= 64) return b200moe::quant_rows(x_bf16, tokens, codes, scales, stream);
   const int64_t n_vec = tokens * (k / 8);
   const unsigned grid = static_cast<unsigned>((n_vec + 255) / 256);
   B200MOE_LAUNCH_PLAIN(quant_mxfp4_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x_bf16), n_vec, k, reinterpret_cast<uint32_t*>(codes), scales);
@@ -262,6 +311,17 @@ extern "C" int b200moe_quant_mxfp4(const void* x_bf16, int64_t tokens, int k, ui
 }
 
 namespace b200moe {
+int quant_rows(const void* x_bf16, int64_t tokens, uint8_t* codes, uint8_t* scales, void* stream) {
+  if (!x_bf16 || !codes || !scales || tokens < 0) return B200MOE_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(codes) & 3) ||
+      (reinterpret_cast<uintptr_t>(scales) & 3))
+    return B200MOE_E_ALIGN;
+  if (tokens == 0) return 0;
+  B200MOE_LAUNCH(quant_rows_kernel, static_cast<unsigned>(tokens), 256, 0, static_cast<cudaStream_t>(stream),
+                 static_cast<const uint4*>(x_bf16), codes, scales);
+  return 0;
+}
+
 int dispatch_rows_done(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids, const int32_t* num_valid,
                        int64_t tokens, int bm, int by_pair, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
                        int32_t* done, void* stream) {

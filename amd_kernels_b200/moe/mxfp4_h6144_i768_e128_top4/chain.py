@@ -72,6 +72,7 @@ class MoeWeights:
     routing_mode: str = "sigmoid_bias"
     shared_weights: object | None = None
     row_major: tuple | None = None  # the checkpoint tensors, kept only on request (the CUDA-core cross-check reads them)
+    router_split: torch.Tensor | None = None  # the gate as three bf16 terms [3, 128, H] for the tensor-core router
     _abi: object = field(default=None, repr=False)
 
     @classmethod
@@ -119,10 +120,13 @@ class MoeWeights:
             if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.device != self.w13.device
                                      or tuple(gate.shape) != (self.num_experts, H)):
                 raise ValueError(f"router_weight: expected contiguous fp32 [{self.num_experts}, {H}] on {self.w13.device}")
+            if gate is not None and self.router_split is None:
+                self.router_split = split_gate(gate)
             self._abi = _lib.Weights(self.w13.data_ptr(), self.w2.data_ptr(),
                                      None if self.correction_bias is None else self.correction_bias.data_ptr(),
                                      self.num_experts, ROUTING_MODES[self.routing_mode],
-                                     self.routed_scaling_factor, None if gate is None else gate.data_ptr())
+                                     self.routed_scaling_factor, None if gate is None else gate.data_ptr(),
+                                     None if gate is None else self.router_split.data_ptr())
         return self._abi
 
 
@@ -393,12 +397,26 @@ def _logits(x, w, router_logits):
         return router_logits.contiguous()
     if w.router_weight is None:
         raise ValueError("needs router_logits= or MoeWeights with router_weight")
-    return router_gemm_partials(x, w.router_weight)
+    w.abi()  # makes the gate's bf16 terms on first use
+    return router_gemm_partials(x, w.router_weight, w.router_split)
 
 
-def router_gemm_partials(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+def split_gate(gate: torch.Tensor) -> torch.Tensor:
+    """fp32 gate [E, 6144] -> its three bf16 terms RN(w), RN(w - w0), RN(w - w0 - w1) as bf16 [3, 128, 6144] (rows from E on
+    zero): the tensor-core router's B operand (reference router_gemm.py:32-44 ``_split3``). Once, at load time."""
+    if gate.dtype != torch.float32 or gate.ndim != 2 or gate.shape[1] != H or not gate.is_contiguous() or gate.shape[0] > E:
+        raise ValueError("expected a contiguous fp32 gate [E <= 128, 6144]")
+    out = torch.empty((3, E, H), dtype=torch.bfloat16, device=gate.device)
+    with torch.cuda.device(gate.device):
+        _lib.check(_lib.load().b200moe_router_split_gate(_ptr(gate), gate.shape[0], _ptr(out), _stream(gate.device)),
+                   "router_split_gate")
+    return out
+
+
+def router_gemm_partials(x: torch.Tensor, gate: torch.Tensor, split: torch.Tensor | None = None) -> torch.Tensor:
     """bf16 x [M, 6144] times the fp32 gate [E, 6144] -> split-K partials as an [M, S, E] view of [S, M, E] (the layout
-    the reference's routers write, router_gemm.py:390-467); ``topk_route`` adds them in split order."""
+    the reference's routers write, router_gemm.py:390-467); ``topk_route`` adds them in split order. With ``split``
+    (``split_gate(gate)``) and 128 tokens or more the product runs on the tensor cores, else on the CUDA cores."""
     if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("expected contiguous BF16 [M,6144]")
     if gate.dtype != torch.float32 or gate.ndim != 2 or gate.shape[1] != H or not gate.is_contiguous():
@@ -407,20 +425,29 @@ def router_gemm_partials(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     m, n_exp = x.shape[0], gate.shape[0]
     splits = int(lib.b200moe_router_splits(m))
     parts = torch.empty((splits, m, n_exp), dtype=torch.float32, device=x.device)
-    _lib.check(lib.b200moe_router_gemm(_ptr(x), _ptr(gate), m, n_exp, splits, _ptr(parts), _stream(x.device)), "router_gemm")
+    if split is not None and m >= 128:
+        _lib.check(lib.b200moe_router_gemm_tc(_ptr(x), _ptr(split), m, n_exp, splits, _ptr(parts),
+                                              _ptr(status_word(x.device)), _stream(x.device)), "router_gemm_tc")
+    else:
+        _lib.check(lib.b200moe_router_gemm(_ptr(x), _ptr(gate), m, n_exp, splits, _ptr(parts), _stream(x.device)),
+                   "router_gemm")
     return parts.permute(1, 0, 2)
 
 
-def router_gemm_quant(x: torch.Tensor, gate: torch.Tensor, shared: bool = False):
-    """One pass over bf16 x [M, 6144]: the split-K logit partials of ``router_gemm_partials``, the row-major MXFP4 operands
-    of ``mxfp4_quant`` and, with ``shared``, the row-major MXFP8 operands of ``shared_quant_rows`` (else None), all with
-    those kernels' bits (reference router_mxfp4_mxfp8_quant_row_scales.py)."""
+def router_gemm_quant(x: torch.Tensor, gate: torch.Tensor, shared: bool = False, split: torch.Tensor | None = None):
+    """The split-K logit partials of ``router_gemm_partials``, the row-major MXFP4 operands of ``mxfp4_quant`` and, with
+    ``shared``, the row-major MXFP8 operands of ``shared_quant_rows`` (else None), all with those kernels' bits (reference
+    router_mxfp4_mxfp8_quant_row_scales.py). Below 128 tokens (or without ``split``) ONE kernel makes one pass over x; from
+    128 tokens on the router runs on the tensor cores (``split`` = ``split_gate(gate)``) with the quantisers beside it."""
     if x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("expected contiguous BF16 [M,6144]")
     if gate.dtype != torch.float32 or gate.ndim != 2 or gate.shape[1] != H or not gate.is_contiguous():
         raise ValueError("expected a contiguous fp32 gate [E, 6144]")
     lib = _lib.load()
     m, n_exp, dev = x.shape[0], gate.shape[0], x.device
+    if split is not None and m >= 128:
+        from .shared_expert import shared_quant_rows
+        return router_gemm_partials(x, gate, split), mxfp4_quant(x), (shared_quant_rows(x) if shared else (None, None))
     splits = int(lib.b200moe_router_splits(m))
     parts = torch.empty((splits, m, n_exp), dtype=torch.float32, device=dev)
     q4 = torch.empty((m, H // 2), dtype=torch.uint8, device=dev)

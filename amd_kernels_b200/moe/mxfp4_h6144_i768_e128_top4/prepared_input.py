@@ -131,8 +131,9 @@ class MoeInputCompact:
 def prepare_mxfp4_moe(x, w) -> MoeInput:
     """One local bf16 [M, 6144] shard prepared before the caller's all-gather (reference prepared_input.py:117-136):
     routing from ``w.router_weight`` (split-K partials added in split order), the routed experts' MXFP4 operands and, with
-    a shared expert, its MXFP8 operands, every scale row-major, all from ONE pass over x (the router GEMM fused with both
-    quantisers). Returns only tensor payloads; the caller owns the gather."""
+    a shared expert, its MXFP8 operands, every scale row-major: below 128 tokens from ONE pass over x (the router GEMM fused
+    with both quantisers), from 128 tokens on with the router on the tensor cores. The payload carries exactly the routing
+    and codes ``mxfp4_moe(x, w)`` computes. Returns only tensor payloads; the caller owns the gather."""
     from .chain import router_gemm_quant, topk_route, variant_for
     if (not isinstance(x, torch.Tensor) or x.ndim != 2 or x.shape[1] != H or x.dtype != torch.bfloat16
             or not x.is_contiguous()):
@@ -140,7 +141,9 @@ def prepare_mxfp4_moe(x, w) -> MoeInput:
     variant_for(x.shape[0])
     if w.router_weight is None:
         raise ValueError("needs MoeWeights with router_weight: MoeWeights.from_row_major(router_weight, ...)")
-    parts, (q, s), (q8, s8) = router_gemm_quant(x, w.router_weight, shared=w.shared_weights is not None)
+    w.abi()  # makes the gate's bf16 terms on first use
+    parts, (q, s), (q8, s8) = router_gemm_quant(x, w.router_weight, shared=w.shared_weights is not None,
+                                                split=w.router_split)
     wt, ids = topk_route(parts, w.correction_bias, w.routed_scaling_factor, w.routing_mode)
     return MoeInput(q, s, wt, ids, q8, s8)
 

@@ -74,6 +74,15 @@ int b200moe_router_splits(int64_t tokens);
 int b200moe_router_gemm(const void* x_bf16, const float* gate, int64_t tokens, int num_experts, int splits,
                         float* partials, void* stream);
 
+/* The same partials on the tensor cores, for 128 tokens and more (MOE/router_gemm.py:32-44 _split3, :48-290 the bf16x3
+ * MMA kernel): b200moe_router_split_gate turns the fp32 gate into its three bf16 terms RN(w), RN(w - w0), RN(w - w0 - w1)
+ * once at load time (split_bf16: bf16 [3][128][6144], rows from num_experts on zero); b200moe_router_gemm_tc multiplies
+ * with tcgen05.mma kind::f16 into fp32 accumulators. Same layout and the same error bound as b200moe_router_gemm (the
+ * bits differ: the sum runs in another order); splits must divide 96. `status` as in the grouped GEMMs. */
+int b200moe_router_split_gate(const float* gate, int num_experts, void* split_bf16, void* stream);
+int b200moe_router_gemm_tc(const void* x_bf16, const void* gate_split_bf16, int64_t tokens, int num_experts, int splits,
+                           float* partials, int32_t* status, void* stream);
+
 /* The router GEMM fused with the input quantisers: one pass over x writes the split-K partials as above and, row-major,
  * the routed experts' MXFP4 operands (codes4 [T][3072], scales4 [T][192], the bits of b200moe_quant_mxfp4) and, when
  * codes8 / scales8 are given, the shared expert's MXFP8 operands ([T][6144], [T][192], the bits of
@@ -315,6 +324,7 @@ typedef struct b200moe_weights {
   int route_mode;
   float route_scale;
   const float* gate;   /* router weight fp32 [num_experts][6144]; needed by b200moe_forward_x only, else may be null */
+  const void* gate_split; /* b200moe_router_split_gate of `gate` (bf16 [3][128][6144]) or null: the tensor-core router */
 } b200moe_weights;
 size_t b200moe_workspace_bytes(int64_t tokens, int num_experts);
 int b200moe_forward(const b200moe_weights* w, const void* x_bf16, const float* logits, int64_t tokens, void* workspace,

@@ -203,15 +203,20 @@ def test_quant_dispatch_equals_quant_then_gather(C, m, bm):
     assert np.array_equal(sa[live], sr[live]) and np.all(sa[~live] == 1)
 
 
-@pytest.mark.parametrize("m", [1, 17, 256, 2049])
-def test_router_gemm_partials_within_the_reference_bound(C, m):
+@pytest.mark.parametrize("m,tensor_cores", [(1, False), (17, False), (256, False), (2049, False), (128, True), (300, True),
+                                            (2049, True), (8192, True)])
+def test_router_gemm_partials_within_the_reference_bound(C, m, tensor_cores):
     """Each split-K partial against the fp64 product: |error| <= 2^-18 * sum|x||w| (the reference's bound for its bf16x3
     router, reference.py:101-111 and tests/moe/.../test_router_rounds.py:29-66), bit-identical on a second run, and the
-    top-4 of the summed partials equals the top-4 of the fp64 logits on decided rows."""
+    top-4 of the summed partials equals the top-4 of the fp64 logits on decided rows. Both forms: fp32 FMAs on the CUDA
+    cores, and the gate as three bf16 terms on the tensor cores (tcgen05.mma kind::f16), incl. a ragged last token block."""
     gen = torch.Generator().manual_seed(m)
     x = torch.randn((m, 6144), generator=gen).bfloat16()
     gate = torch.randn((128, 6144), generator=gen) / 6144 ** 0.5
-    parts = C.router_gemm_partials(x.cuda(), gate.cuda())          # [M, S, E] view of [S, M, E]
+    split = C.split_gate(gate.cuda()) if tensor_cores else None
+    if tensor_cores:  # the three terms add up to the gate exactly (each remainder of a round-to-nearest is representable)
+        assert torch.equal(split.float().sum(0).cpu(), gate)
+    parts = C.router_gemm_partials(x.cuda(), gate.cuda(), split)   # [M, S, E] view of [S, M, E]
     splits = parts.shape[1]
     assert parts.shape == (m, splits, 128) and parts.stride(2) == 1 and parts.stride(1) == m * 128
     xd = x.double().reshape(m, splits, -1)
@@ -220,7 +225,9 @@ def test_router_gemm_partials_within_the_reference_bound(C, m):
     bound = torch.stack([xd[:, k].abs() @ wd[:, k].abs().t() for k in range(splits)], 1)
     err = (parts.cpu().double() - exact).abs()
     assert bool((err <= 2.0 ** -18 * bound).all()), float((err / bound).max())
-    assert torch.equal(parts, C.router_gemm_partials(x.cuda(), gate.cuda()))
+    assert torch.equal(parts, C.router_gemm_partials(x.cuda(), gate.cuda(), split))
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
     bias = torch.zeros(128)
     wt, ids = C.topk_route(parts, bias.cuda(), 2.0, "sigmoid_bias")
     wr, ir, vals = orc.route_sigmoid_bias(exact.sum(1).numpy(), bias.numpy(), 2.0)
