@@ -9,6 +9,12 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
+
+def lib_path(inter: int = 768) -> str:
+    """The library built for intermediate size ``inter``: 768 (the i768 package) or 1536 (its TP2 sibling shape)."""
+    return LIB_PATH if inter == 768 else os.path.join(HERE, f"libb200moe_i{inter}.so")
+
+
 E_ARG, E_ALIGN, E_DRIVER, E_TOO_LARGE = -1, -2, -3, -4
 DEV_TIMEOUT, DEV_BAD_INDEX = 1, 2
 ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX = 0, 1
@@ -76,25 +82,26 @@ SIGNATURES = {
     "b200moe_forward_host": (c_int, [POINTER(Weights), _P, _P, c_int64, _P, _P, _P, c_size_t, _P, _P, _P, _P, _P]),
 }
 
-_lib = None
+_libs: dict = {}
 
 
-def load() -> ctypes.CDLL:
-    """The loaded library with typed entry points. Raises RuntimeError when it is absent or unloadable."""
-    global _lib
-    if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m amd_kernels_b200.build` "
+def load(inter: int = 768) -> ctypes.CDLL:
+    """The loaded library (for intermediate size ``inter``) with typed entry points. Raises RuntimeError when it is absent
+    or unloadable."""
+    if inter not in _libs:
+        path = lib_path(inter)
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: build it with `python -m amd_kernels_b200.build` "
                                "(nvcc, sm_100a). This package has no CPU or PyTorch fallback.")
         try:
-            lib = ctypes.CDLL(LIB_PATH)
+            lib = ctypes.CDLL(path)
         except OSError as exc:  # pragma: no cover - depends on the machine
-            raise RuntimeError(f"cannot load {LIB_PATH}: {exc}") from exc
+            raise RuntimeError(f"cannot load {path}: {exc}") from exc
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
-        _lib = lib
-    return _lib
+        _libs[inter] = lib
+    return _libs[inter]
 
 
 def check(code: int, what: str) -> None:

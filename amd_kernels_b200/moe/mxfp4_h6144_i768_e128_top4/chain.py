@@ -74,6 +74,15 @@ class MoeWeights:
     row_major: tuple | None = None  # the checkpoint tensors, kept only on request (the CUDA-core cross-check reads them)
     router_split: torch.Tensor | None = None  # the gate as three bf16 terms [3, 128, H] for the tensor-core router
     _abi: object = field(default=None, repr=False)
+    INTERMEDIATE = I  # the served shape's intermediate size; the i1536 sibling package pins 1536
+
+    @property
+    def intermediate(self) -> int:
+        return self.w13.shape[1] * 64  # 128-row tiles of 64 gate + 64 up rows
+
+    def lib(self):
+        """The library built for this shape's intermediate size."""
+        return _lib.load(self.intermediate)
 
     @classmethod
     def from_row_major(cls, router_weight, correction_bias, w13, w13_scale, w2, w2_scale, *, shared=None,
@@ -81,7 +90,8 @@ class MoeWeights:
         """Checkpoint layout (row-major uint8 MXFP4 codes / e8m0 scales, gate rows then up rows) -> the kernels'
         layouts. ``routing_mode``: "sigmoid_bias" (the reference's rule) or "softmax" (top-4 of the softmax,
         renormalised). ``shared``: the MXFP8 shared expert's ``SharedWeights`` (or None: routed experts only)."""
-        reason = unsupported_reason(w13, w13_scale, w2, w2_scale, None, None, None, None, routed_only=True)
+        inter = cls.INTERMEDIATE
+        reason = unsupported_reason(w13, w13_scale, w2, w2_scale, None, None, None, None, routed_only=True, inter=inter)
         if reason is not None:
             raise ValueError(reason)
         if shared is not None and not hasattr(shared, "stream"):
@@ -90,12 +100,12 @@ class MoeWeights:
             raise ValueError(f"routing_mode must be one of {sorted(ROUTING_MODES)}")
         if not w13.is_cuda:
             raise ValueError("weights must be CUDA tensors")
-        lib = _lib.load()
+        lib = _lib.load(inter)
         n_exp = w13.shape[0]
         dev = w13.device
         w13, w13_scale, w2, w2_scale = (t.contiguous() for t in (w13, w13_scale, w2, w2_scale))
-        w13t = torch.empty((n_exp, 12, 24, 17408), dtype=torch.uint8, device=dev)
-        w2t = torch.empty((n_exp, 48, 3, 17408), dtype=torch.uint8, device=dev)
+        w13t = torch.empty((n_exp, 2 * inter // 128, 24, 17408), dtype=torch.uint8, device=dev)
+        w2t = torch.empty((n_exp, 48, inter // 256, 17408), dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             _lib.check(lib.b200moe_preshuffle_w13(_ptr(w13), _ptr(w13_scale), n_exp, _ptr(w13t), _stream(dev)),
                        "preshuffle_w13")
@@ -131,9 +141,11 @@ class MoeWeights:
 
 
 def unsupported_reason(w13, w13_scale, w2, w2_scale, shared_w13, shared_s13, shared_w2, shared_s2,
-                       swiglu=(1.702, 7.0, 1.0), *, routed_only=False) -> str | None:
+                       swiglu=(1.702, 7.0, 1.0), *, routed_only=False, inter=I) -> str | None:
     """None when ``MoeWeights.from_row_major`` takes these checkpoint-layout tensors, else the reason
-    (reference __init__.py:19-35). ``routed_only`` skips the shared-expert tensors (a layer without one)."""
+    (reference __init__.py:19-35). ``routed_only`` skips the shared-expert tensors (a layer without one); ``inter``: the
+    intermediate size of the served shape."""
+    I = inter  # noqa: E741,N806
     ref = (1.702, 7.0, 1.0)
     if any(abs(a - b) > 1e-6 for a, b in zip(swiglu, ref)):
         return f"needs SwiGLU-OAI (alpha, limit, beta) {ref}, got {tuple(swiglu)}"
@@ -268,9 +280,9 @@ def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_nex
     ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first. (From about 13000 tokens' worth of rows
     the library runs the CTA-pair kernel of ``grouped_gemm1_pair``; same bits.)"""
     dev = xq_sorted.device
-    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
-    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
-    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant(_ptr(w.w13), w.num_experts, _ptr(xq_sorted),
+    hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(w.lib().b200moe_gemm1_swiglu_quant(_ptr(w.w13), w.num_experts, _ptr(xq_sorted),
                                                       _ptr(sfx), _ptr(sort.block_expert), _ptr(sort.num_valid),
                                                       sort.max_rows, sort.bm, _ptr(hq), _ptr(sfh),
                                                       _ptr(w.w2) if prefetch_next else None,
@@ -284,9 +296,9 @@ def grouped_gemm1_pair(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
     if sort.bm != 128:
         raise ValueError("the CTA-pair GEMM1 serves block height 128")
     dev = xq_sorted.device
-    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
-    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
-    _lib.check(_lib.load().b200moe_gemm1_swiglu_quant_pair(_ptr(w.w13), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
+    hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(w.lib().b200moe_gemm1_swiglu_quant_pair(_ptr(w.w13), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
                                                            _ptr(sort.block_expert), _ptr(sort.num_valid), sort.max_rows,
                                                            _ptr(hq), _ptr(sfh), _ptr(status_word(dev)), _stream(dev)),
                "gemm1_swiglu_quant_pair")
@@ -298,13 +310,13 @@ def grouped_gemm12(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, slots=None,
     same bits as ``grouped_gemm1`` followed by ``grouped_gemm2`` (reference gemm12_a4w4.py:24). ``done``: the per-block
     completion counts, int32 [rows / bm], zero on entry (allocated when not given)."""
     dev = xq_sorted.device
-    hq = torch.empty((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
-    sfh = torch.empty((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
+    hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
     if done is None:
         done = torch.zeros(sort.max_rows // sort.bm, dtype=torch.int32, device=dev)
     if slots is None:
         slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
-    _lib.check(_lib.load().b200moe_gemm12(_ptr(w.w13), _ptr(w.w2), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
+    _lib.check(w.lib().b200moe_gemm12(_ptr(w.w13), _ptr(w.w2), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
                                           _ptr(sort.block_expert), _ptr(sort.num_valid), _ptr(sort.sorted_ids),
                                           _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens, _ptr(hq),
                                           _ptr(sfh), _ptr(done), _ptr(slots), _ptr(status_word(dev)), _stream(dev)),
@@ -317,7 +329,7 @@ def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):
     dev = hq.device
     if slots is None:
         slots = torch.empty((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
-    _lib.check(_lib.load().b200moe_gemm2_weighted(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
+    _lib.check(w.lib().b200moe_gemm2_weighted(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
                                                   _ptr(sort.block_expert), _ptr(sort.num_valid), _ptr(sort.sorted_ids),
                                                   _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens,
                                                   _ptr(slots), _ptr(status_word(dev)), _stream(dev)), "gemm2_weighted")
@@ -329,7 +341,7 @@ def grouped_gemm2_peer(hq, sfh, sort: SortBuffers, w: MoeWeights, row_rank, row_
     """GEMM2 whose result rows go straight into the slot buffers of the ranks that own the pairs (expert parallel):
     ``row_rank`` / ``row_pair`` int32 [4 * sort.tokens], ``peer_ptrs`` a ctypes array of ``world`` device pointers."""
     dev = hq.device
-    _lib.check(_lib.load().b200moe_gemm2_weighted_peer(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
+    _lib.check(w.lib().b200moe_gemm2_weighted_peer(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
                                                        _ptr(sort.block_expert), _ptr(sort.num_valid),
                                                        _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), sort.max_rows,
                                                        sort.bm, sort.tokens, _ptr(row_rank), _ptr(row_pair), peer_ptrs,
@@ -343,9 +355,9 @@ def simt_gemm1(x_quant, sort: SortBuffers, w: MoeWeights, rows=None):
         raise ValueError("needs MoeWeights.from_row_major(..., keep_row_major=True)")
     codes, scales = x_quant
     dev = codes.device
-    hq = torch.zeros((sort.max_rows, I // 2), dtype=torch.uint8, device=dev)
-    sfh = torch.zeros((sort.max_rows // sort.bm, I // 128, 512), dtype=torch.uint8, device=dev)
-    _lib.check(_lib.load().b200moe_gemm1_simt(_ptr(w.row_major[0]), _ptr(w.row_major[1]), _ptr(codes), _ptr(scales),
+    hq = torch.zeros((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.zeros((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(w.lib().b200moe_gemm1_simt(_ptr(w.row_major[0]), _ptr(w.row_major[1]), _ptr(codes), _ptr(scales),
                                               _ptr(sort.sorted_ids), _ptr(sort.block_expert), _ptr(sort.num_valid),
                                               _ptr(rows), 0 if rows is None else rows.numel(), sort.max_rows, sort.bm,
                                               sort.tokens, _ptr(hq), _ptr(sfh), _stream(dev)), "gemm1_simt")
@@ -359,7 +371,7 @@ def simt_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, rows=None, slots=None)
     dev = hq.device
     if slots is None:
         slots = torch.zeros((sort.tokens, TOPK, H), dtype=torch.bfloat16, device=dev)
-    _lib.check(_lib.load().b200moe_gemm2_simt(_ptr(w.row_major[2]), _ptr(w.row_major[3]), _ptr(hq), _ptr(sfh),
+    _lib.check(w.lib().b200moe_gemm2_simt(_ptr(w.row_major[2]), _ptr(w.row_major[3]), _ptr(hq), _ptr(sfh),
                                               _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), _ptr(sort.block_expert),
                                               _ptr(sort.num_valid), _ptr(rows), 0 if rows is None else rows.numel(),
                                               sort.max_rows, sort.bm, sort.tokens, _ptr(slots), _stream(dev)), "gemm2_simt")
@@ -515,7 +527,7 @@ def mxfp4_moe(x, w, *, return_partials=False, router_logits=None):
 def _routed_layer(x, w, router_logits, slots, out):
     """One C-ABI call for the routed layer on the current stream: ``b200moe_forward`` when the caller hands fp32 logits,
     ``b200moe_forward_x`` (router GEMM fused with the input quantiser inside the call) when it hands only ``x``."""
-    lib = _lib.load()
+    lib = w.lib()
     n, dev = x.shape[0], x.device
     if router_logits is not None:
         if router_logits.shape != (n, w.num_experts) or router_logits.dtype != torch.float32:
@@ -536,7 +548,9 @@ def _routed_layer(x, w, router_logits, slots, out):
 
 def set_wait_limit_ns(ns: int) -> None:
     """How long a device-side wait may last on the current device before the kernel gives up with status 1 (default 2 s)."""
-    _lib.check(_lib.load().b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
+    for inter in (768, 1536):  # every build of the library this process has loaded keeps its own limit
+        if inter == 768 or inter in _lib._libs:
+            _lib.check(_lib.load(inter).b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
 
 
 WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000, 14000)  # one-launch GEMMs, one size per block height, the two-CTA and the CTA-pair GEMM1

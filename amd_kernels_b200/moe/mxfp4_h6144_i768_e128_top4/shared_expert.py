@@ -58,10 +58,16 @@ class SharedWeights:
     w2: torch.Tensor
     s2: torch.Tensor | None
     stream: object
+    INTERMEDIATE = I  # the i1536 sibling package pins 1536
+
+    @property
+    def intermediate(self) -> int:
+        return self.w13.shape[0] * 64
 
     @classmethod
     def from_row_major(cls, w13, s13, w2, s2):
         """From row-major e4m3 [N, K] weights and e8m0 [N, K / 32] scales (gate rows, then up rows in ``w13``)."""
+        I = cls.INTERMEDIATE  # noqa: E741,N806
         if tuple(w13.shape) != (2 * I, H) or tuple(w2.shape) != (H, I):
             raise ValueError(f"shared weights: needs [{2 * I}, {H}] and [{H}, {I}]")
         if tuple(s13.shape) != (2 * I, H // 32) or tuple(s2.shape) != (H, I // 32):
@@ -72,11 +78,11 @@ class SharedWeights:
             raise ValueError("shared weights and scales must be 1-byte types (e4m3 codes, e8m0 scales)")
         dev = w13.device
         c13, b13, c2, b2 = (t.contiguous().view(torch.uint8) for t in (w13, s13, w2, s2))
-        w13t = torch.empty((12, 48, RECORD_BYTES), dtype=torch.uint8, device=dev)
-        w2t = torch.empty((48, 6, RECORD_BYTES), dtype=torch.uint8, device=dev)
+        w13t = torch.empty((2 * I // 128, 48, RECORD_BYTES), dtype=torch.uint8, device=dev)
+        w2t = torch.empty((48, I // 128, RECORD_BYTES), dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-            _lib.check(_lib.load().b200moe_preshuffle_shared(_ptr(c13), _ptr(b13), _ptr(c2), _ptr(b2), _ptr(w13t),
+            _lib.check(_lib.load(I).b200moe_preshuffle_shared(_ptr(c13), _ptr(b13), _ptr(c2), _ptr(b2), _ptr(w13t),
                                                              _ptr(w2t), st), "preshuffle_shared")
         return cls(w13t, None, w2t, None, side_stream(dev))
 
@@ -132,7 +138,7 @@ def shared_expert(x: torch.Tensor | None, w: SharedWeights, *, x_quant=None, str
     ``stream``: launch there instead of on the current stream; the buffers still come from the current stream's
     allocator pool and are recorded on ``stream``."""
     from .chain import status_word, variant_for
-    lib = _lib.load()
+    lib = _lib.load(w.intermediate)
     if x_quant is None:
         _check_x(x)
         n, dev = x.shape[0], x.device

@@ -33,7 +33,9 @@ extern "C" {
 #endif
 
 #define B200MOE_H 6144
+#ifndef B200MOE_I /* intermediate size of the build: 768 (libb200moe.so) or 1536 (libb200moe_i1536.so, the TP2 sibling shape) */
 #define B200MOE_I 768
+#endif
 #define B200MOE_E 128
 #define B200MOE_TOPK 4
 #define B200MOE_MAX_TOKENS 87381 /* MOE/chain.py:13-18, variant_for rejects more */
@@ -268,8 +270,8 @@ int b200moe_reduce_slots_add_rmsnorm_quant(const void* slots_bf16, const void* s
  * up rows like the routed ones. */
 int b200moe_preshuffle_shared(const uint8_t* w13, const uint8_t* w13_scale, const uint8_t* w2, const uint8_t* w2_scale,
                               uint8_t* w13t, uint8_t* w2t, void* stream);
-#define B200MOE_SHARED_W13T_BYTES (12 * 48 * 17408)
-#define B200MOE_SHARED_W2T_BYTES (48 * 6 * 17408)
+#define B200MOE_SHARED_W13T_BYTES ((2 * B200MOE_I / 128) * 48 * 17408)
+#define B200MOE_SHARED_W2T_BYTES (48 * (B200MOE_I / 128) * 17408)
 
 /* The dense block height the shared expert uses at T tokens: 16 / 32 / 64 up to that many tokens, else 128. */
 int b200moe_shared_block_rows(int64_t tokens);

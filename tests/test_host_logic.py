@@ -24,10 +24,13 @@ def declared_functions():
 def test_library_exports_every_declared_symbol():
     names = declared_functions()
     assert len(names) >= 18
-    lib = ctypes.CDLL(_lib.LIB_PATH)
-    for name in names:
-        assert hasattr(lib, name), name
+    for inter in (768, 1536):  # both builds of the sources: the i768 package's library and its i1536 sibling's
+        lib = ctypes.CDLL(_lib.lib_path(inter))
+        for name in names:
+            assert hasattr(lib, name), (inter, name)
     assert set(_lib.SIGNATURES) == set(names), "the ctypes table and the header disagree"
+    # the builds differ where the intermediate size enters: scratch for h (codes + scale atoms per sorted row)
+    assert _lib.load(1536).b200moe_workspace_bytes(4096, 128) > _lib.load(768).b200moe_workspace_bytes(4096, 128)
     lib = _lib.load()
     assert lib.b200moe_arch() == b"sm_100a" and lib.b200moe_version() >= 1
 
