@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(256) gemm2_simt_kernel(const uint8_t* __restri
     const int64_t wrow = static_cast<int64_t>(e) * kH + n;
     const uint4* wq = reinterpret_cast<const uint4*>(w2 + wrow * (kI / 2));
     float acc = 0.0f;
-    if (lane < kI / 32) acc = dot32(wq[lane], hs + lane * 32, e8m0_value(s2[wrow * (kI / 32) + lane]));
+    for (int blk = lane; blk < kI / 32; blk += 32)
+      acc += dot32(wq[blk], hs + blk * 32, e8m0_value(s2[wrow * (kI / 32) + blk]));
     acc = warp_sum(acc);
     if (lane == 0) slots[(token * kTopK + slot) * kH + n] = __float2bfloat16_rn(acc * wt);
   }

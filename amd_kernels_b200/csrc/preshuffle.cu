@@ -16,7 +16,8 @@ __device__ __forceinline__ int w13_source_row(int t, int r) {
   return (g & 1) ? kI + i : i;
 }
 
-// One CTA per (tile row, m-tile, expert); thread j moves 16-byte chunk j of the row and scale byte j.
+// One CTA per (tile row, m-tile, expert) of at least K_BYTES / 16 threads; thread j moves 16-byte chunk j of the row and
+// scale byte j.
 template <int K_BYTES, int TILES_M, bool IS_W13>
 __global__ void preshuffle_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                                   uint8_t* __restrict__ out) {
@@ -46,7 +47,7 @@ extern "C" int b200moe_preshuffle_w13(const uint8_t* w13, const uint8_t* w13_sca
   using namespace b200moe;
   if (!w13 || !w13_scale || !w13t || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w13) & 15) || (reinterpret_cast<uintptr_t>(w13t) & 15)) return B200MOE_E_ALIGN;
-  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kH / 2, kW13Tiles, true>), dim3(128, kW13Tiles, num_experts), 192, 0, static_cast<cudaStream_t>(stream), w13, w13_scale, w13t);
+  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kH / 2, kW13Tiles, true>), dim3(128, kW13Tiles, num_experts), (kH / 2 / 16 + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream), w13, w13_scale, w13t);
   return 0;
 }
 
@@ -55,6 +56,6 @@ extern "C" int b200moe_preshuffle_w2(const uint8_t* w2, const uint8_t* w2_scale,
   using namespace b200moe;
   if (!w2 || !w2_scale || !w2t || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
   if ((reinterpret_cast<uintptr_t>(w2) & 15) || (reinterpret_cast<uintptr_t>(w2t) & 15)) return B200MOE_E_ALIGN;
-  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kI / 2, kW2Tiles, false>), dim3(128, kW2Tiles, num_experts), 32, 0, static_cast<cudaStream_t>(stream), w2, w2_scale, w2t);
+  B200MOE_LAUNCH_PLAIN((preshuffle_kernel<kI / 2, kW2Tiles, false>), dim3(128, kW2Tiles, num_experts), (kI / 2 / 16 + 31) / 32 * 32, 0, static_cast<cudaStream_t>(stream), w2, w2_scale, w2t);
   return 0;
 }

@@ -69,6 +69,10 @@ def test_tensor_core_gemms_equal_cuda_core_gemms(C, sibling, tokens, bm):
     sa, sr = (atoms_to_rowmajor(t.cpu().numpy(), bm)[:nv][live] for t in (sfh, sfh_r))
     assert (sa != sr).mean() < 1e-4
     check_against_oracle(slots.float().cpu().numpy().sum(1), slots_r.float().cpu().numpy().sum(1))
+    # and against the CPU oracle directly, so the two GPU paths cannot be wrong together
+    pick = np.unique(np.linspace(0, tokens - 1, 4).astype(int))
+    xq_np, xs_np = orc.quant_mxfp4(orc.bf16_to_f32(xb))
+    check_against_oracle(slots.float().cpu().numpy()[pick].sum(1), oracle_slots(xq_np, xs_np, raw, ids, wts, tokens=pick).sum(1))
     if bm == 128 and C._lib.load(I2).b200moe_gemm1_pair_supported():
         p_h, p_s = C.grouped_gemm1_pair(xs, sfx, sb, w)
         torch.cuda.synchronize()
