@@ -30,6 +30,11 @@ struct Workspace {
 int dispatch_rows_done(const uint8_t* codes, const uint8_t* scales, const int32_t* sorted_ids, const int32_t* num_valid,
                        int64_t tokens, int bm, int by_pair, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx,
                        int32_t* done, void* stream);
+int prep_small(const float* partials, int64_t stride_t, int64_t stride_s, int splits, const float* bias, int64_t tokens,
+               int num_experts, int mode, float scale, int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids,
+               float* sorted_w, int32_t* block_expert, int32_t* num_valid, const void* x_bf16, const uint8_t* q4,
+               const uint8_t* s4, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, int32_t* done, int n_done,
+               void* stream);
 int quant_rows(const void* x_bf16, int64_t tokens, uint8_t* codes, uint8_t* scales, void* stream);
 int set_wait_limit_routed(unsigned long long ns);
 int set_wait_limit_shared(unsigned long long ns);
@@ -94,12 +99,13 @@ extern "C" int b200moe_set_wait_limit_ns(uint64_t ns) {
 }
 
 namespace b200moe {
+constexpr int64_t kSmallTokens = 32;  // up to here a layer call is three launches: preparation, both GEMMs, reduce
 // sorted, gathered, quantised rows are in the workspace: the grouped GEMMs and the reduce
 static int experts_and_reduce(const b200moe_weights* w, const Workspace& ws, int64_t tokens, void* slots_bf16,
                               void* out_bf16, int32_t* status, void* stream) {
   const int ne = w->num_experts;
   int r;
-  if (tokens <= 32) {  // small batches: both grouped GEMMs in one persistent launch (measured faster there only)
+  if (tokens <= kSmallTokens) {  // small batches: both grouped GEMMs in one persistent launch (measured faster there only)
     if ((r = b200moe_gemm12(w->w13t, w->w2t, ne, ws.xq_sorted, ws.sfx, ws.block_expert, ws.num_valid, ws.sorted_ids,
                             ws.sorted_w, ws.rows, ws.bm, tokens, ws.hq, ws.sfh, ws.done, slots_bf16, status, stream)))
       return r;
@@ -136,6 +142,13 @@ extern "C" int b200moe_forward_x(const b200moe_weights* w, const void* x_bf16, i
                                             stream))) {  // one pass over x: logit partials and the MXFP4 operands, row-major
     return r;
   }
+  if (tokens <= kSmallTokens && ne >= 4) {  // routing on the partials, sort and gather of the quantised rows in one launch
+    if ((r = prep_small(ws.partials, ne, tokens * ne, splits, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.bm, ws.w,
+                        ws.ids, ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid, nullptr, ws.q4, ws.s4, ws.rows,
+                        ws.xq_sorted, ws.sfx, ws.done, static_cast<int>(ws.rows / ws.bm), stream)))
+      return r;
+    return experts_and_reduce(w, ws, tokens, slots_bf16, out_bf16, status, stream);
+  }
   if ((r = b200moe_route_sort_partials(ws.partials, ne, tokens * ne, splits, w->bias, tokens, ne, w->route_mode,
                                        w->route_scale, ws.bm, ws.w, ws.ids, ws.sorted_ids, ws.sorted_w, ws.block_expert,
                                        ws.num_valid, ws.scratch, stream)))
@@ -157,6 +170,13 @@ extern "C" int b200moe_forward(const b200moe_weights* w, const void* x_bf16, con
   Workspace ws = carve(static_cast<uint8_t*>(workspace), tokens, ne);
   if (workspace_bytes < ws.bytes) return B200MOE_E_ARG;
   int r;
+  if (tokens <= kSmallTokens && ne >= 4) {  // routing, sort, quantisation and gather in one launch
+    if ((r = prep_small(logits, ne, 0, 1, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.bm, ws.w, ws.ids,
+                        ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid, x_bf16, nullptr, nullptr, ws.rows,
+                        ws.xq_sorted, ws.sfx, ws.done, static_cast<int>(ws.rows / ws.bm), stream)))
+      return r;
+    return experts_and_reduce(w, ws, tokens, slots_bf16, out_bf16, status, stream);
+  }
   if ((r = b200moe_route_sort(logits, w->bias, tokens, ne, w->route_mode, w->route_scale, ws.bm, ws.w, ws.ids,
                               ws.sorted_ids, ws.sorted_w, ws.block_expert, ws.num_valid, ws.scratch, stream)))
     return r;

@@ -142,4 +142,60 @@ __device__ __forceinline__ float swiglu_oai(float g, float u) {
 // byte offset of scale j (0..3) of row r (0..127) inside a 512-byte scale atom
 __device__ __host__ __forceinline__ int atom_offset(int r, int j) { return (r & 31) * 16 + (r >> 5) * 4 + j; }
 
+// 256 threads (t = 0..255, whole warps) quantise one bf16 row of kH values to MXFP4: 3072 code bytes to `dst` and the 192
+// scale bytes into the row's cells of its block's scale atoms (`sdst` = atom 0 + atom_offset(row in block, 0)). The three
+// 16-byte loads of a thread are in flight together. `src` null: a padding row (zero codes, the scale byte of a zero block).
+__device__ __forceinline__ void quant_row_to_atoms(const uint4* src, uint32_t* dst, uint8_t* sdst, int t) {
+  constexpr int kIters = kH / 8 / 256;  // 3
+  const int lane = t & 31;
+  if (src == nullptr) {
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) {
+      const int idx = it * 256 + t;
+      dst[idx] = 0u;
+      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = 0x01010101u;
+    }
+    return;
+  }
+  uint4 raw[kIters];
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) raw[it] = __ldcg(src + it * 256 + t);
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    const int idx = it * 256 + t;
+    const uint32_t rr[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(rr[j] << 16);
+      v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const int e = quark_even_e8m0(amax);
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);  // 2^(127-e), exact
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
+    dst[idx] = packed;
+    // 4 lanes share a 32-element block, 16 lanes one scale atom's 4 bytes: lanes 0 and 16 gather their neighbours' bytes
+    uint32_t sc = static_cast<uint32_t>(e);
+    sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
+    sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
+    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = sc;
+  }
+}
+
+// The same for a row that is already quantised (row-major codes / scales of its token): copy and re-lay the scales.
+__device__ __forceinline__ void copy_row_to_atoms(const uint8_t* codes, const uint8_t* scales, uint32_t* dst, uint8_t* sdst,
+                                                  int t) {
+  constexpr int kIters = kH / 8 / 256;  // 3 x 4 bytes of codes per thread
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) dst[it * 256 + t] = __ldcg(reinterpret_cast<const uint32_t*>(codes) + it * 256 + t);
+  if (t < kH / 128) *reinterpret_cast<uint32_t*>(sdst + t * kAtomBytes) = __ldcg(reinterpret_cast<const uint32_t*>(scales) + t);
+}
+
 }  // namespace b200moe

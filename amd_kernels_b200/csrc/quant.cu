@@ -123,58 +123,17 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
                                                              uint8_t* __restrict__ sfx, int32_t* __restrict__ done,
                                                              int n_done) {
   pdl_enter(x, sorted_ids, num_valid);
-  constexpr int kIters = kH / 8 / 256;  // 3
   {  // the per-block completion counts of the one-launch GEMM1+GEMM2 start every call at zero
     const int64_t z = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (done != nullptr && z < n_done) done[z] = 0;
   }
-  const int lane = threadIdx.x & 31;
   const int64_t row = blockIdx.x;
   if (row >= __ldcg(num_valid)) return;
   const int64_t token = __ldcg(sorted_ids + row) & 0x00ffffff;
   uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + row * (kH / 2));
   const int r = static_cast<int>(row & ((1 << bm_shift) - 1));
   uint8_t* sdst = sfx + (row >> bm_shift) * (kH / 128) * kAtomBytes + atom_offset(r, 0);
-  if (token >= tokens) {  // a padding row: zero codes, the scale byte of an all-zero block
-#pragma unroll
-    for (int it = 0; it < kIters; ++it) {
-      const int idx = it * 256 + threadIdx.x;
-      dst[idx] = 0u;
-      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = 0x01010101u;
-    }
-    return;
-  }
-  const uint4* src = x + token * (kH / 8);
-  uint4 raw[kIters];
-#pragma unroll
-  for (int it = 0; it < kIters; ++it) raw[it] = __ldcg(src + it * 256 + threadIdx.x);
-#pragma unroll
-  for (int it = 0; it < kIters; ++it) {
-    const int idx = it * 256 + threadIdx.x;
-    const uint32_t rr[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      v[2 * j] = __uint_as_float(rr[j] << 16);
-      v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const int e = quark_even_e8m0(amax);
-    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);  // 2^(127-e), exact
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
-    dst[idx] = packed;
-    // 4 lanes share a 32-element block, 16 lanes one scale atom's 4 bytes: lanes 0 and 16 gather their neighbours' bytes
-    uint32_t sc = static_cast<uint32_t>(e);
-    sc |= __shfl_down_sync(0xffffffffu, sc, 4) << 8;
-    sc |= __shfl_down_sync(0xffffffffu, sc, 8) << 16;
-    if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sdst + (idx >> 4) * kAtomBytes) = sc;
-  }
+  quant_row_to_atoms(token >= tokens ? nullptr : x + token * (kH / 8), dst, sdst, threadIdx.x);
 }
 
 // Expert-parallel dispatch fused with the quantisation: one CTA per send row quantises the pair's token row and stores

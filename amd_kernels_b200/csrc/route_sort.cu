@@ -126,7 +126,8 @@ struct SortShared {
 __device__ __forceinline__ void place_chunk(SortShared& sh, int e, float wv, int64_t q, int64_t tokens, int num_experts,
                                             int bm_shift, const int32_t* __restrict__ cta_counts,
                                             int32_t* __restrict__ sorted_ids, float* __restrict__ sorted_w,
-                                            int32_t* __restrict__ block_expert, int32_t* __restrict__ num_valid) {
+                                            int32_t* __restrict__ block_expert, int32_t* __restrict__ num_valid,
+                                            int* pos_out = nullptr) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bm = 1 << bm_shift;
   for (int i = tid; i < 32 * (kMaxE + 1); i += kChunk) (&sh.warp_cnt[0][0])[i] = 0;
@@ -203,6 +204,7 @@ __device__ __forceinline__ void place_chunk(SortShared& sh, int e, float wv, int
     const int pos = sh.start[e] + sh.base[e] + sh.warp_cnt[warp][e] + rank;
     sorted_ids[pos] = static_cast<int>(q >> 2) | (static_cast<int>(q & 3) << 24);
     sorted_w[pos] = wv;
+    if (pos_out != nullptr) *pos_out = pos;
   }
   // padding rows and the block -> expert list: experts dealt round-robin to the chunks, then to the warps
   for (int x = blockIdx.x + warp * gridDim.x; x < num_experts; x += 32 * gridDim.x) {
@@ -277,6 +279,71 @@ __global__ void __launch_bounds__(kChunk) route_sort_kernel(const float* __restr
   float wv = 0.0f;
   if (q < tokens * kTopK) { e = s_ids[q]; wv = s_w[q]; }
   place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, nullptr, sorted_ids, sorted_w, block_expert, num_valid);
+}
+
+// Up to 32 tokens, ONE launch prepares the grouped GEMMs' input: every CTA of a small grid routes all tokens and sorts all
+// pairs by itself (a few microseconds of redundant work, and identical stores of the same values to the routing tables, in
+// exchange for a launch and a grid-wide dependency less), then the CTAs share the sorted rows among them: four rows at a
+// time per CTA, 256 threads each, quantised from the bf16 row (GATHER false) or copied from row-major quantised rows
+// (GATHER true: the router inside the call has quantised the tokens already). CTA 0 also zeroes `done`.
+constexpr int kPrepMaxRows = 2048;  // 32 tokens x 4 pairs, every pair alone in a 16-row block
+template <int MODE, bool GATHER>
+__global__ void __launch_bounds__(kChunk) prep_small_kernel(const float* __restrict__ logits, int64_t stride_t,
+                                                            int64_t stride_s, int splits, const float* __restrict__ bias,
+                                                            int tokens, int num_experts, float scale, int bm_shift,
+                                                            float* __restrict__ out_w, int32_t* __restrict__ out_ids,
+                                                            int32_t* __restrict__ sorted_ids, float* __restrict__ sorted_w,
+                                                            int32_t* __restrict__ block_expert,
+                                                            int32_t* __restrict__ num_valid, const uint4* __restrict__ x,
+                                                            const uint8_t* __restrict__ q4, const uint8_t* __restrict__ s4,
+                                                            uint8_t* __restrict__ xq_sorted, uint8_t* __restrict__ sfx,
+                                                            int32_t* __restrict__ done, int n_done) {
+  pdl_enter(logits, bias, x, q4, s4);
+  __shared__ SortShared sh;
+  __shared__ int s_ids[kTopK * kFusedRouteTokens];
+  __shared__ float s_w[kTopK * kFusedRouteTokens];
+  __shared__ int16_t s_token[kPrepMaxRows];  // token of a sorted row, -1 for a padding row
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (blockIdx.x == 0)
+    for (int z = threadIdx.x; z < n_done; z += kChunk) done[z] = 0;
+  for (int i = threadIdx.x; i < kPrepMaxRows; i += kChunk) s_token[i] = -1;
+  if (warp < tokens) {
+    float w[4];
+    int id[4];
+    route_token<MODE>(logits + static_cast<int64_t>(warp) * stride_t, stride_s, splits, bias, num_experts, scale, lane, w, id);
+    if (lane < 4) {
+      float wv = w[0];
+      int iv = id[0];
+#pragma unroll
+      for (int r = 1; r < 4; ++r)
+        if (lane == r) { wv = w[r]; iv = id[r]; }
+      s_ids[warp * 4 + lane] = iv;
+      s_w[warp * 4 + lane] = wv;
+      if (blockIdx.x == 0) {
+        out_w[warp * 4 + lane] = wv;
+        out_ids[warp * 4 + lane] = iv;
+      }
+    }
+  }
+  __syncthreads();
+  const int q = threadIdx.x;
+  int e = -1, pos = -1;
+  float wv = 0.0f;
+  if (q < tokens * kTopK) { e = s_ids[q]; wv = s_w[q]; }
+  place_chunk(sh, e, wv, q, tokens, num_experts, bm_shift, nullptr, sorted_ids, sorted_w, block_expert, num_valid, &pos);
+  if (pos >= 0 && pos < kPrepMaxRows) s_token[pos] = static_cast<int16_t>(q >> 2);
+  __syncthreads();
+  const int rows = min(sh.start[num_experts], kPrepMaxRows);
+  const int sub = threadIdx.x >> 8, t = threadIdx.x & 255;  // four rows at a time per CTA
+  for (int row = blockIdx.x * 4 + sub; row < rows; row += gridDim.x * 4) {
+    const int token = s_token[row];
+    uint32_t* dst = reinterpret_cast<uint32_t*>(xq_sorted + static_cast<int64_t>(row) * (kH / 2));
+    const int r = row & ((1 << bm_shift) - 1);
+    uint8_t* sdst = sfx + static_cast<int64_t>(row >> bm_shift) * (kH / 128) * kAtomBytes + atom_offset(r, 0);
+    if (token < 0) quant_row_to_atoms(nullptr, dst, sdst, t);
+    else if (GATHER) copy_row_to_atoms(q4 + static_cast<int64_t>(token) * (kH / 2), s4 + static_cast<int64_t>(token) * (kH / 32), dst, sdst, t);
+    else quant_row_to_atoms(x + static_cast<int64_t>(token) * (kH / 8), dst, sdst, t);
+  }
 }
 
 // bm = 1 (no padding) serves the expert-parallel send order: pairs grouped by destination rank
@@ -378,6 +445,41 @@ extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_
   return b200moe_route_sort_partials(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, bm, out_w, out_ids,
                                      sorted_ids, sorted_w, block_expert, num_valid, scratch, stream);
 }
+
+// Routing, sort and the gather of quantised rows in one launch, up to 32 tokens (see prep_small_kernel). Either x (bf16
+// rows, quantised here) or q4 / s4 (rows quantised before) is given.
+namespace b200moe {
+int prep_small(const float* partials, int64_t stride_t, int64_t stride_s, int splits, const float* bias, int64_t tokens,
+               int num_experts, int mode, float scale, int bm, float* out_w, int32_t* out_ids, int32_t* sorted_ids,
+               float* sorted_w, int32_t* block_expert, int32_t* num_valid, const void* x_bf16, const uint8_t* q4,
+               const uint8_t* s4, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, int32_t* done, int n_done,
+               void* stream) {
+  if (!partials || !out_w || !out_ids || !sorted_ids || !sorted_w || !block_expert || !num_valid || !xq_sorted || !sfx)
+    return B200MOE_E_ARG;
+  if ((x_bf16 == nullptr) == (q4 == nullptr) || (q4 != nullptr && s4 == nullptr)) return B200MOE_E_ARG;
+  if (tokens < 1 || tokens > kFusedRouteTokens || num_experts < 4 || num_experts > kMaxE || splits < 1 || bm != 16 ||
+      max_rows > kPrepMaxRows)
+    return B200MOE_E_ARG;
+  if (mode != B200MOE_ROUTE_SIGMOID_BIAS && mode != B200MOE_ROUTE_SOFTMAX) return B200MOE_E_ARG;
+  const int shift = shift_of(bm);
+  const unsigned grid = static_cast<unsigned>(max_rows / 4 < 1 ? 1 : (max_rows / 4 > 148 ? 148 : max_rows / 4));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* x = static_cast<const uint4*>(x_bf16);
+#define B200MOE_PREP(M, G)                                                                                              \
+  B200MOE_LAUNCH((prep_small_kernel<M, G>), grid, kChunk, 0, s, partials, stride_t, stride_s, splits, bias,             \
+                 static_cast<int>(tokens), num_experts, scale, shift, out_w, out_ids, sorted_ids, sorted_w, block_expert, \
+                 num_valid, x, q4, s4, xq_sorted, sfx, done, n_done)
+  if (mode == B200MOE_ROUTE_SIGMOID_BIAS) {
+    if (q4) B200MOE_PREP(B200MOE_ROUTE_SIGMOID_BIAS, true);
+    else B200MOE_PREP(B200MOE_ROUTE_SIGMOID_BIAS, false);
+  } else {
+    if (q4) B200MOE_PREP(B200MOE_ROUTE_SOFTMAX, true);
+    else B200MOE_PREP(B200MOE_ROUTE_SOFTMAX, false);
+  }
+#undef B200MOE_PREP
+  return 0;
+}
+}  // namespace b200moe
 
 // ------------------------------------------------------------------------------------------------ allocation-free sort
 // Some hosts of this library may not allocate device memory around a call: a serving engine that hands every plugin a

@@ -232,9 +232,9 @@ class Layer:
         return sum(n) / len(n)
 
     def launches_per_step(self):
-        # up to 32 tokens: route+sort, quantise+gather, both GEMMs in one launch, reduce; above: routing and sort apart
-        # (plus a count pass above 256), quantise+gather, two GEMMs, reduce
-        return 4 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
+        # up to 32 tokens: preparation (route + sort + quantise + gather), both GEMMs in one launch, reduce; above: routing,
+        # sort (plus a count pass above 256 tokens), quantise+gather (two kernels at 128-row blocks), two GEMMs, reduce
+        return 3 if self.tokens <= 32 else (6 if self.tokens <= 256 else (7 if self.tokens <= 1728 else 8))
 
     def replay(self, i):
         self.graphs[i % len(self.graphs)].replay()
