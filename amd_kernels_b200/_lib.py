@@ -43,6 +43,9 @@ SIGNATURES = {
     "b200moe_quant_mxfp4": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "b200moe_permute_scratch_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_permute": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P]),
+    "b200moe_permute_live": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
+    "b200moe_ep_dest": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, _P, _P]),
+    "b200moe_ep_offsets": (c_int, [_P, c_int, c_int, _P, _P, _P, _P]),
     "b200moe_permute_static": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P]),
     "b200moe_route_sort": (c_int, [_P, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P, _P, _P]),
@@ -53,6 +56,7 @@ SIGNATURES = {
     "b200moe_gemm1_swiglu_quant": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, c_int, _P, _P, _P, _P, _P]),
     "b200moe_gemm1_pair_supported": (c_int, []),
     "b200moe_gemm1_swiglu_quant_pair": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
+    "b200moe_gemm1_swiglu_quant_wide": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
     "b200moe_gemm2_weighted": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_weighted_peer": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int,
                                             c_int64, _P, _P]),

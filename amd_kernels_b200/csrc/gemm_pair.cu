@@ -98,6 +98,31 @@ __device__ __forceinline__ void drain_tcgen05_pair(uint32_t bar) {
   while (!mbar_try_wait(bar, 0) && global_timer() - t0 < limit) {}
 }
 
+// One (token row, 32-column group of the intermediate): SwiGLU-OAI of the 32 gate / up accumulators, the block maximum, the
+// E8M0 byte and the 32 E2M1 codes -> one 16-byte store of codes and one scale byte; everything thread-local.
+__device__ __forceinline__ void swiglu_quant_store(const uint32_t (&gv)[32], const uint32_t (&uv)[32], uint8_t* hq,
+                                                   uint8_t* sfh, int64_t row, int b, int tr, int grp) {
+  float h[32];
+  float amax = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    h[k] = swiglu_oai(__uint_as_float(gv[k]), __uint_as_float(uv[k]));
+    amax = fmaxf(amax, fabsf(h[k]));
+  }
+  const int sc = quark_even_e8m0(amax);
+  const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
+  uint32_t words[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t acc_w = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
+    words[wd] = acc_w;
+  }
+  *reinterpret_cast<uint4*>(hq + row * (kI / 2) + grp * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+  sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(tr, grp & 3)] = static_cast<uint8_t>(sc);
+}
+
 // what a row block is to the pair schedule
 enum : uint8_t { kBlockSkip = 0, kBlockSingle = 1, kBlockPair = 2 };
 
@@ -338,30 +363,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1
       ++ui;
       if (!have_rows) continue;
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        float h[32];
-        float amax = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          h[k] = swiglu_oai(__uint_as_float(acc[2 * g][k]), __uint_as_float(acc[2 * g + 1][k]));
-          amax = fmaxf(amax, fabsf(h[k]));
-        }
-        const int sc = quark_even_e8m0(amax);
-        const float inv = __uint_as_float(static_cast<uint32_t>(254 - sc) << 23);
-        uint32_t words[4];
-#pragma unroll
-        for (int wd = 0; wd < 4; ++wd) {
-          uint32_t acc_w = 0;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            acc_w |= cvt_e2m1x2(h[8 * wd + 2 * k] * inv, h[8 * wd + 2 * k + 1] * inv) << (8 * k);
-          words[wd] = acc_w;
-        }
-        const int grp = 4 * tp + 2 * half + g;  // 32-column group of the intermediate, 0..23
-        *reinterpret_cast<uint4*>(hq + row * (kI / 2) + grp * 16) = make_uint4(words[0], words[1], words[2], words[3]);
-        sfh[(static_cast<int64_t>(b) * (kI / 128) + (grp >> 2)) * kAtomBytes + atom_offset(tr, grp & 3)] =
-            static_cast<uint8_t>(sc);
-      }
+      for (int g = 0; g < 2; ++g)
+        swiglu_quant_store(acc[2 * g], acc[2 * g + 1], hq, sfh, row, b, tr, 4 * tp + 2 * half + g);
     }
   }
 
@@ -371,6 +374,215 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ one CTA, N = 256
+// The same 256-column unit on ONE CTA: M = 128 token rows (one row block) x N = 256 weight rows (two W13 tiles) per
+// tcgen05.mma.cta_group::1. Every block is a unit, so an expert's odd last block costs nothing extra; the price is that the
+// CTA stages both weight tiles itself (51 KB per stage, 4 stages). Roles as in the pair kernel: warp 0 producer, warp 1
+// MMA issue (and TMEM), warps 2 and 11 the scale copies, warps 3-10 the register-only epilogue.
+struct WideCfg {
+  static constexpr int kStages = 4;
+  static constexpr int kTokOff = 0;
+  static constexpr int kWOff = 128 * 128;            // 256 weight rows x 128 bytes: tile 2*tp, then tile 2*tp+1
+  static constexpr int kSfTokOff = 3 * 128 * 128;
+  static constexpr int kSfWLoOff = kSfTokOff + 2 * kAtomBytes;
+  static constexpr int kSfWHiOff = kSfWLoOff + 2 * kAtomBytes;
+  static constexpr int kStageBytes = kSfWHiOff + 2 * kAtomBytes;  // 52224
+  static constexpr int kThreads = PairCfg::kThreads;
+  static constexpr int kSfSets = 8;
+  static constexpr int kSfCol = 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTilePairs = kW13Tiles / 2;
+  static constexpr uint32_t kTx = 3 * 128 * 128 + 6 * kAtomBytes;
+};
+
+__device__ __forceinline__ void tc_mma_mxf4_wide(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
+                                                 uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %7};\nmov.b64 db, {%2, %7};\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate), "n"(kOperandDescHi)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(WideCfg::kThreads, 1)
+    gemm1_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_sfx,
+                      const __grid_constant__ CUtensorMap map_wc, const __grid_constant__ CUtensorMap map_ws,
+                      const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid,
+                      uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh, int32_t* status, int num_experts,
+                      int max_blocks) {
+  using C = WideCfg;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[C::kStages];
+  __shared__ __align__(8) uint64_t bar_empty[C::kStages];
+  __shared__ __align__(8) uint64_t bar_sf[C::kStages];
+  __shared__ __align__(8) uint64_t bar_tfull;
+  __shared__ __align__(8) uint64_t bar_tempty;
+  __shared__ __align__(8) uint64_t bar_drain[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abort_v = &abort_flag;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_sf[s]), 2);  // the two scale-copy threads
+    }
+    mbar_init(smem_u32(&bar_tfull), 1);
+    mbar_init(smem_u32(&bar_tempty), 8);  // one arrival per epilogue warp
+    mbar_init(smem_u32(&bar_drain[0]), 1);
+    mbar_init(smem_u32(&bar_drain[1]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(static_cast<uint32_t>(C::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  pdl_wait();
+  launder(block_expert);
+  launder(num_valid);
+  int n_blocks = __ldcg(num_valid) / 128;
+  if (n_blocks < 0 || n_blocks > max_blocks) {
+    if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
+    n_blocks = 0;
+  }
+  const int total = n_blocks * C::kTilePairs, stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = first; u < total && ok; u += stride) {
+        const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+        int e = __ldcg(block_expert + b);
+        if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
+          atomicExch(status, B200MOE_DEV_BAD_INDEX);
+          e = 0;
+        }
+        // rows of the weight matrix seen as [records * 136][128 bytes]: 128 rows of codes, then 8 rows of scales
+        const int rec_lo = ((e * kW13Tiles + 2 * tp) * kK1Tiles) * 136, rec_hi = rec_lo + kK1Tiles * 136;
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]), base = tiles + s * C::kStageBytes;
+          mbar_arrive_expect_tx(full, C::kTx);
+          tma_load_2d(base + C::kWOff, &map_wc, 0, rec_lo + kt * 136, full);
+          tma_load_2d(base + C::kWOff + 128 * 128, &map_wc, 0, rec_hi + kt * 136, full);
+          tma_load_2d(base + C::kTokOff, &map_x, kt * 128, b * 128, full);
+          tma_load_2d(base + C::kSfWLoOff, &map_ws, 0, rec_lo + kt * 136 + 128, full);
+          tma_load_2d(base + C::kSfWHiOff, &map_ws, 0, rec_hi + kt * 136 + 128, full);
+          tma_load_2d(base + C::kSfTokOff, &map_sfx, 0, (b * (kH / 128) + 2 * kt) * 4, full);
+        }
+      }
+      if (!ok) drain_copies(bar_full, it, C::kStages);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      // E2M1 x E2M1, UE8M0 scales, M = 128 token rows, N = 256 weight rows
+      constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (1u << 23) |
+                                  (static_cast<uint32_t>(128 >> 4) << 24);
+      constexpr uint32_t kId0 = kIdesc, kId1 = kIdesc | (2u << 29) | (2u << 4);
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int u = first; u < total && ok; u += stride, ++ui) {
+        if (!mbar_wait(smem_u32(&bar_tempty), (ui & 1u) ^ 1u, abort_v, status)) break;
+        tc_fence_after();
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
+          if (!mbar_wait(smem_u32(&bar_sf[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
+          const uint32_t x_lo = lo + (C::kTokOff >> 4), w_lo = lo + (C::kWOff >> 4);
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          tc_mma_mxf4_wide(tmem_base, x_lo, w_lo, kId0, t_sft, t_sfw, static_cast<uint32_t>(kt != 0));
+          tc_mma_mxf4_wide(tmem_base, x_lo + 2, w_lo + 2, kId1, t_sft, t_sfw, 1u);
+          tc_mma_mxf4_wide(tmem_base, x_lo + 4, w_lo + 4, kId0, t_sft + 4, t_sfw + 8, 1u);
+          tc_mma_mxf4_wide(tmem_base, x_lo + 6, w_lo + 6, kId1, t_sft + 4, t_sfw + 8, 1u);
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&bar_tfull));
+      }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
+    }
+  } else if (warp == 2 || warp == 11) {
+    // ---------------------------------------------------------------- scale copies (three of the six atoms each)
+    if (lane == 0) {
+      const bool head = warp == 2;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = first; u < total && ok; u += stride) {
+        for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          if (head) {
+            tc_cp_scales_lo(t_sft, lo + (C::kSfTokOff >> 4));
+            tc_cp_scales_lo(t_sft + 4, lo + ((C::kSfTokOff + kAtomBytes) >> 4));
+            tc_cp_scales_lo(t_sfw, lo + (C::kSfWLoOff >> 4));
+          } else {
+            tc_cp_scales_lo(t_sfw + 4, lo + (C::kSfWHiOff >> 4));
+            tc_cp_scales_lo(t_sfw + 8, lo + ((C::kSfWLoOff + kAtomBytes) >> 4));
+            tc_cp_scales_lo(t_sfw + 12, lo + ((C::kSfWHiOff + kAtomBytes) >> 4));
+          }
+          tc_commit(smem_u32(&bar_sf[s]));
+        }
+      }
+      if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 3..10)
+    const int q = warp & 3;
+    const int half = ((warp - 3) >> 2) & 1;
+    const int tr = q * 32 + lane;
+    uint32_t ui = 0;
+    for (int u = first; u < total; u += stride, ++ui) {
+      const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+      const int64_t row = static_cast<int64_t>(b) * 128 + tr;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull), ui & 1u, abort_v, status))) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + 128u * half + (static_cast<uint32_t>(q * 32) << 16);
+      uint32_t acc[4][32];
+      tc_ld32_nowait(t_acc, acc[0]);
+      tc_ld32_nowait(t_acc + 32, acc[1]);
+      tc_ld32_nowait(t_acc + 64, acc[2]);
+      tc_ld32_nowait(t_acc + 96, acc[3]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      tc_fence_before();  // the accumulator sits in registers: hand it back, the next unit's MMAs run under the arithmetic
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty));
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+        swiglu_quant_store(acc[2 * g], acc[2 * g + 1], hq, sfh, row, b, tr, 4 * tp + 2 * half + g);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(C::kTmemCols))
                  : "memory");
   }
@@ -426,6 +638,36 @@ static int resident_pairs() {
 int set_wait_limit_pair(unsigned long long ns) { return set_wait_limit_here(ns); }
 
 }  // namespace b200moe
+
+extern "C" int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted,
+                                               const uint8_t* sfx, const int32_t* block_expert, const int32_t* num_valid,
+                                               int64_t max_rows, uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
+  using namespace b200moe;
+  using C = WideCfg;
+  if (!w13t || !xq_sorted || !sfx || !block_expert || !num_valid || !hq || !sfh || !status) return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || max_rows % 128) return B200MOE_E_ARG;
+  if (misaligned(w13t, 16) || misaligned(xq_sorted, 16) || misaligned(sfx, 16) || misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  CUtensorMap mx, msf, mwc, mws;
+  int r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), 128);
+  if (r) return r;
+  const uint64_t sf_rows = static_cast<uint64_t>(max_rows / 128) * (kH / 128) * 4;
+  if ((r = make_flat_map(&msf, sfx, sf_rows, 8))) return r;
+  const uint64_t w_rows = static_cast<uint64_t>(num_experts) * kW13Tiles * kK1Tiles * 136;
+  if ((r = make_flat_map(&mwc, w13t, w_rows, 128))) return r;
+  if ((r = make_flat_map(&mws, w13t, w_rows, 8))) return r;
+  static PerDeviceOnce once;
+  const int rc = once.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(gemm1_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  });
+  if (rc) return rc;
+  const int64_t max_units = max_rows / 128 * C::kTilePairs;
+  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  B200MOE_LAUNCH(gemm1_wide_kernel, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc, mws,
+                 block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
+  return 0;
+}
 
 extern "C" int b200moe_gemm1_pair_supported(void) { return b200moe::resident_pairs() > 0 ? 1 : 0; }
 

@@ -948,8 +948,8 @@ __global__ void __launch_bounds__(256, 1)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-constexpr int64_t kPairFromRows = 60000;  // sorted rows (about 13000 tokens) from which GEMM1 runs on CTA pairs
-constexpr int64_t kDualFromRows = 36000;  // upper bound of sorted rows from which GEMM1 runs two CTAs per SM
+constexpr int64_t kWideFromRows = 20000;  // sorted rows (about 3000 tokens) from which GEMM1 uses 256 weight rows per MMA
+constexpr int64_t kDualFromRows = 36000;  // sorted rows from which the 128-column GEMM1 runs two CTAs per SM
 template <int MODE, int BM, bool DUAL = false>
 static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
@@ -1066,10 +1066,10 @@ extern "C" int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, 
       misaligned(sfh, 16))
     return B200MOE_E_ALIGN;
   if (max_rows == 0) return 0;
-  // Very large batches: CTA pairs (256 token rows x 256 weight rows per MMA); measured 313 vs 327 us at 16384 tokens,
-  // 202 vs 196 us at 8192, where every second unit is an expert's odd last block and half of the pair idles.
-  if (bm == 128 && max_rows >= kPairFromRows && b200moe_gemm1_pair_supported())
-    return b200moe_gemm1_swiglu_quant_pair(w13t, num_experts, xq_sorted, sfx, block_expert, num_valid, max_rows, hq, sfh,
+  // Prefill sizes: 256 weight rows per MMA on one CTA (twice the math per issued instruction). Measured, GEMM1 alone, us:
+  // 4096 tokens 127 (128-column kernel 129), 8192 tokens 183 (197; CTA pairs 199), 16384 tokens 312 (320; pairs 320).
+  if (bm == 128 && max_rows >= kWideFromRows)
+    return b200moe_gemm1_swiglu_quant_wide(w13t, num_experts, xq_sorted, sfx, block_expert, num_valid, max_rows, hq, sfh,
                                            status, stream);
   CUtensorMap mx;
   const int r = make_map(&mx, xq_sorted, kH / 2, static_cast<uint64_t>(max_rows), static_cast<uint32_t>(bm));

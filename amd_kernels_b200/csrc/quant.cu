@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(256) quant_dispatch_kernel(const uint4* __rest
 }
 
 // Expert-parallel dispatch fused with the quantisation: one CTA per send row quantises the pair's token row and stores
-// codes (3072 contiguous bytes), row-major scales (192 bytes) and a 16-byte meta record {expert id on the destination,
-// routing weight bits, source pair, source rank} straight into the destination rank's receive buffers (peer mappings over
+// codes (3072 contiguous bytes), row-major scales (192 bytes) and four meta words {expert id on the destination, routing
+// weight bits, source pair, source rank} (column arrays [4][capacity]) straight into the destination rank's receive buffers (peer mappings over
 // NVLink, or local memory for rows that stay). Plain stores, no waits; the caller orders the ranks afterwards.
 struct PushArgs {
   uint8_t* codes[8];
@@ -209,8 +209,12 @@ __global__ void __launch_bounds__(256) quant_push_kernel(const uint4* __restrict
   if (threadIdx.x == 0) {
     const int e = ids[token * kTopK + slot];
     const int local = a.interleaved ? e / a.world : e % a.experts_per_rank;
-    *reinterpret_cast<int4*>(a.meta[d] + row * 4) =
-        make_int4(local, __float_as_int(send_w[i]), static_cast<int>(token * kTopK + slot), a.rank);
+    // four column arrays [4][capacity]: the receiver hands columns straight to its sort and to GEMM2's row tables
+    int32_t* m = a.meta[d] + row;
+    m[0] = local;
+    m[a.capacity] = __float_as_int(send_w[i]);
+    m[2 * a.capacity] = static_cast<int>(token * kTopK + slot);
+    m[3 * a.capacity] = a.rank;
   }
 }
 

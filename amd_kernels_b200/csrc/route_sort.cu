@@ -100,12 +100,16 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
   }
 }
 
+// `limit` (may be null): a device count of the pairs that are live; pairs from there on are ignored whatever their id (the
+// expert-parallel receive buffers are sorted at full capacity without the arrived count ever reaching the host).
 __global__ void __launch_bounds__(kChunk) permute_count_kernel(const int32_t* __restrict__ ids, int64_t pairs,
-                                                               int num_experts, int32_t* __restrict__ cta_counts) {
-  pdl_enter(ids);
+                                                               int num_experts, int32_t* __restrict__ cta_counts,
+                                                               const int32_t* __restrict__ limit) {
+  pdl_enter(ids, limit);
   __shared__ int hist[kMaxE];
   if (threadIdx.x < kMaxE) hist[threadIdx.x] = 0;
   __syncthreads();
+  if (limit != nullptr) pairs = min(pairs, static_cast<int64_t>(__ldcg(limit)));
   const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
   if (q < pairs) {
     const int e = __ldcg(ids + q);
@@ -225,10 +229,12 @@ __global__ void __launch_bounds__(kChunk) permute_place_kernel(const int32_t* __
                                                                int32_t* __restrict__ sorted_ids,
                                                                float* __restrict__ sorted_w,
                                                                int32_t* __restrict__ block_expert,
-                                                               int32_t* __restrict__ num_valid) {
-  pdl_enter(ids, w, cta_counts);
+                                                               int32_t* __restrict__ num_valid,
+                                                               const int32_t* __restrict__ limit) {
+  pdl_enter(ids, w, cta_counts, limit);
   __shared__ SortShared sh;
-  const int64_t pairs = tokens * kTopK;
+  int64_t pairs = tokens * kTopK;
+  if (limit != nullptr) pairs = min(pairs, static_cast<int64_t>(__ldcg(limit)));
   const int64_t q = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
   int e = -1;
   float wv = 0.0f;
@@ -346,6 +352,46 @@ __global__ void __launch_bounds__(kChunk) prep_small_kernel(const float* __restr
   }
 }
 
+// Expert-parallel send plan, part 1: the destination rank of every (token, slot) pair and the number of pairs per rank.
+// One CTA; integer counts, so the result does not depend on the order of the atomics.
+__global__ void __launch_bounds__(kChunk) ep_dest_kernel(const int32_t* __restrict__ ids, int64_t pairs, int world,
+                                                         int experts_per_rank, int interleaved,
+                                                         int32_t* __restrict__ dest, int64_t* __restrict__ counts) {
+  pdl_enter(ids);
+  __shared__ int hist[8];
+  if (threadIdx.x < 8) hist[threadIdx.x] = 0;
+  __syncthreads();
+  for (int64_t q = threadIdx.x; q < pairs; q += kChunk) {
+    const int e = __ldcg(ids + q);
+    int d = interleaved ? e % world : e / experts_per_rank;
+    if (e < 0 || d >= world) d = -1;
+    dest[q] = d;
+    if (d >= 0) atomicAdd(&hist[d], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < world) counts[threadIdx.x] = hist[threadIdx.x];
+}
+
+// Part 2, after the ranks exchanged their counts (matrix[s][d] = pairs rank s sends to rank d): where this rank's segment
+// starts in its own send order and in every destination's receive buffers, and how many pairs it receives.
+__global__ void ep_offsets_kernel(const int64_t* __restrict__ matrix, int world, int rank, int32_t* __restrict__ seg_start,
+                                  int64_t* __restrict__ dst_base, int32_t* __restrict__ recv_pairs) {
+  pdl_enter(matrix);
+  const int d = threadIdx.x;
+  if (d < world) {
+    int64_t before = 0, base = 0;
+    for (int k = 0; k < d; ++k) before += __ldcg(matrix + rank * world + k);
+    for (int s = 0; s < rank; ++s) base += __ldcg(matrix + s * world + d);
+    seg_start[d] = static_cast<int32_t>(before);
+    dst_base[d] = base;
+  }
+  if (d == 0) {
+    int64_t n = 0;
+    for (int s = 0; s < world; ++s) n += __ldcg(matrix + s * world + rank);
+    *recv_pairs = static_cast<int32_t>(n);
+  }
+}
+
 // bm = 1 (no padding) serves the expert-parallel send order: pairs grouped by destination rank
 static int shift_of(int bm) { return bm == 1 ? 0 : bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1; }
 
@@ -392,6 +438,13 @@ extern "C" int b200moe_block_rows(int64_t tokens) {
 extern "C" int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
                                int32_t* sorted_ids, float* sorted_w, int32_t* block_expert, int32_t* num_valid,
                                int32_t* scratch, void* stream) {
+  return b200moe_permute_live(ids, w, tokens, num_experts, bm, nullptr, sorted_ids, sorted_w, block_expert, num_valid, scratch,
+                              stream);
+}
+
+extern "C" int b200moe_permute_live(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
+                                    const int32_t* live_pairs, int32_t* sorted_ids, float* sorted_w, int32_t* block_expert,
+                                    int32_t* num_valid, int32_t* scratch, void* stream) {
   using namespace b200moe;
   if (!ids || !w || !sorted_ids || !sorted_w || !block_expert || !num_valid) return B200MOE_E_ARG;
   if (tokens < 1 || tokens > B200MOE_MAX_TOKENS || num_experts < 1 || num_experts > kMaxE) return B200MOE_E_ARG;
@@ -402,9 +455,9 @@ extern "C" int b200moe_permute(const int32_t* ids, const float* w, int64_t token
   if (chunks > 1 && !scratch) return B200MOE_E_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (chunks > 1) {
-    B200MOE_LAUNCH(permute_count_kernel, chunks, kChunk, 0, s, ids, pairs, num_experts, scratch);
+    B200MOE_LAUNCH(permute_count_kernel, chunks, kChunk, 0, s, ids, pairs, num_experts, scratch, live_pairs);
   }
-  B200MOE_LAUNCH(permute_place_kernel, chunks, kChunk, 0, s, ids, w, tokens, num_experts, shift, chunks > 1 ? scratch : nullptr, sorted_ids, sorted_w, block_expert, num_valid);
+  B200MOE_LAUNCH(permute_place_kernel, chunks, kChunk, 0, s, ids, w, tokens, num_experts, shift, chunks > 1 ? scratch : nullptr, sorted_ids, sorted_w, block_expert, num_valid, live_pairs);
   return 0;
 }
 
@@ -444,6 +497,26 @@ extern "C" int b200moe_route_sort(const float* logits, const float* bias, int64_
                                   void* stream) {
   return b200moe_route_sort_partials(logits, num_experts, 0, 1, bias, tokens, num_experts, mode, scale, bm, out_w, out_ids,
                                      sorted_ids, sorted_w, block_expert, num_valid, scratch, stream);
+}
+
+extern "C" int b200moe_ep_dest(const int32_t* ids, int64_t tokens, int world, int experts_per_rank, int interleaved,
+                               int32_t* dest, int64_t* counts, void* stream) {
+  using namespace b200moe;
+  if (!ids || !dest || !counts || tokens < 1 || tokens > B200MOE_MAX_TOKENS || world < 1 || world > 8 || experts_per_rank < 1)
+    return B200MOE_E_ARG;
+  B200MOE_LAUNCH(ep_dest_kernel, 1, kChunk, 0, static_cast<cudaStream_t>(stream), ids, tokens * kTopK, world, experts_per_rank,
+                 interleaved, dest, counts);
+  return 0;
+}
+
+extern "C" int b200moe_ep_offsets(const int64_t* matrix, int world, int rank, int32_t* seg_start, int64_t* dst_base,
+                                  int32_t* recv_pairs, void* stream) {
+  using namespace b200moe;
+  if (!matrix || !seg_start || !dst_base || !recv_pairs || world < 1 || world > 8 || rank < 0 || rank >= world)
+    return B200MOE_E_ARG;
+  B200MOE_LAUNCH(ep_offsets_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), matrix, world, rank, seg_start, dst_base,
+                 recv_pairs);
+  return 0;
 }
 
 // Routing, sort and the gather of quantised rows in one launch, up to 32 tokens (see prep_small_kernel). Either x (bf16

@@ -206,8 +206,10 @@ class SortBuffers:
         return self.sorted_ids.shape[0]
 
 
-def moe_sort(topk_ids: torch.Tensor, topk_weights: torch.Tensor, bm: int, num_experts: int = E) -> SortBuffers:
-    """ids int32 [M, 4], weights fp32 [M, 4] -> expert-sorted, block-padded rows in pair order."""
+def moe_sort(topk_ids: torch.Tensor, topk_weights: torch.Tensor, bm: int, num_experts: int = E,
+             live_pairs: torch.Tensor | None = None) -> SortBuffers:
+    """ids int32 [M, 4], weights fp32 [M, 4] -> expert-sorted, block-padded rows in pair order. ``live_pairs`` (a device
+    int32 scalar): only the first that many pairs count, whatever the ids behind them say."""
     if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32 or topk_ids.shape != topk_weights.shape \
             or topk_ids.ndim != 2 or topk_ids.shape[1] != TOPK:
         raise ValueError("expected int32 ids and fp32 weights of shape [M, 4]")
@@ -220,9 +222,9 @@ def moe_sort(topk_ids: torch.Tensor, topk_weights: torch.Tensor, bm: int, num_ex
                       bm, m)
     scratch_bytes = int(lib.b200moe_permute_scratch_bytes(m, num_experts))
     scratch = torch.empty(max(scratch_bytes // 4, 1), dtype=torch.int32, device=dev)
-    _lib.check(lib.b200moe_permute(_ptr(topk_ids.contiguous()), _ptr(topk_weights.contiguous()), m, num_experts, bm,
-                                   _ptr(buf.sorted_ids), _ptr(buf.sorted_weights), _ptr(buf.block_expert),
-                                   _ptr(buf.num_valid), _ptr(scratch), _stream(dev)), "permute")
+    _lib.check(lib.b200moe_permute_live(_ptr(topk_ids.contiguous()), _ptr(topk_weights.contiguous()), m, num_experts, bm,
+                                        _ptr(live_pairs), _ptr(buf.sorted_ids), _ptr(buf.sorted_weights),
+                                        _ptr(buf.block_expert), _ptr(buf.num_valid), _ptr(scratch), _stream(dev)), "permute")
     return buf
 
 
@@ -277,8 +279,8 @@ def route_sort(logits: torch.Tensor, w: "MoeWeights", bm: int | None = None):
 
 def grouped_gemm1(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights, prefetch_next: bool = False):
     """GEMM1 + SwiGLU-OAI + MXFP4 requantisation on tcgen05 -> (h codes [rows, 384], h scale atoms [rows/bm, 6, 512]).
-    ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first. (From about 13000 tokens' worth of rows
-    the library runs the CTA-pair kernel of ``grouped_gemm1_pair``; same bits.)"""
+    ``prefetch_next``: also ask L2 for the W2 tiles the following GEMM2 reads first. (From about 3000 tokens' worth of rows
+    the library runs the 256-column kernel of ``grouped_gemm1_wide``; same bits.)"""
     dev = xq_sorted.device
     hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
@@ -302,6 +304,21 @@ def grouped_gemm1_pair(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
                                                            _ptr(sort.block_expert), _ptr(sort.num_valid), sort.max_rows,
                                                            _ptr(hq), _ptr(sfh), _ptr(status_word(dev)), _stream(dev)),
                "gemm1_swiglu_quant_pair")
+    return hq, sfh
+
+
+def grouped_gemm1_wide(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
+    """``grouped_gemm1`` at block height 128 with 256 weight rows per MMA on one CTA (128 token rows x 256 weight rows x 64):
+    the same h codes and scale atoms."""
+    if sort.bm != 128:
+        raise ValueError("the wide GEMM1 serves block height 128")
+    dev = xq_sorted.device
+    hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
+    sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
+    _lib.check(w.lib().b200moe_gemm1_swiglu_quant_wide(_ptr(w.w13), w.num_experts, _ptr(xq_sorted), _ptr(sfx),
+                                                       _ptr(sort.block_expert), _ptr(sort.num_valid), sort.max_rows,
+                                                       _ptr(hq), _ptr(sfh), _ptr(status_word(dev)), _stream(dev)),
+               "gemm1_swiglu_quant_wide")
     return hq, sfh
 
 
@@ -553,7 +570,7 @@ def set_wait_limit_ns(ns: int) -> None:
             _lib.check(_lib.load(inter).b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
 
 
-WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000, 14000)  # one-launch GEMMs, one size per block height, the two-CTA and the CTA-pair GEMM1
+WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000)  # one-launch GEMMs, one size per block height, the 256-column GEMM1
 
 
 def warm_up_mxfp4_moe(w, *, partials=False, workers=None):

@@ -93,7 +93,8 @@ class PeerBuffers:
     """Buffers of one rank that every other rank of the node can store into (torch symmetric memory: virtual-memory
     handles mapped with access for the local device; the stores themselves are plain peer stores over NVLink):
     ``slots`` bf16 [pairs, 6144] where GEMM2 on any rank deposits this rank's result rows, and the receive buffers of
-    the dispatch (codes, row-major scales, meta) with room for every pair of every rank (the worst routing skew)."""
+    the dispatch (codes, row-major scales, meta as four column arrays) with room for every pair of every rank (the worst
+    routing skew)."""
 
     def __init__(self, max_pairs: int, group=None):
         import ctypes
@@ -101,7 +102,7 @@ class PeerBuffers:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         self.max_pairs, self.capacity = max_pairs, max_pairs * world
         shapes = {"slots": ((max_pairs, H), torch.bfloat16), "codes": ((self.capacity, H // 2), torch.uint8),
-                  "scales": ((self.capacity, H // 32), torch.uint8), "meta": ((self.capacity, 4), torch.int32)}
+                  "scales": ((self.capacity, H // 32), torch.uint8), "meta": ((4, self.capacity), torch.int32)}
         self.local, self.ptrs, self._handles = {}, {}, []
         dev = torch.device("cuda", torch.cuda.current_device())
         for name, (shape, dtype) in shapes.items():
@@ -149,24 +150,31 @@ class ExpertParallelMoe:
             raise ValueError(f"needs {experts // self.world} local experts on each of {self.world} ranks")
         self.bias, self.mode, self.scale, self.placement, self.experts = bias, routing_mode, float(scale), placement, experts
         self.last_recv_rows, self._recv_rows = 0, None
-        if self.peer is not None:
-            self._ranks = torch.arange(self.world, device="cuda")
-            self._rows = torch.arange(self.peer.capacity, device="cuda")
+        if self.peer is not None:  # the send plan lives on the device: nothing of it is read by the host
+            dev = torch.device("cuda", torch.cuda.current_device())
+            self._dest = torch.empty(self.peer.max_pairs, dtype=torch.int32, device=dev)
+            self._counts = torch.zeros(self.world, dtype=torch.int64, device=dev)
+            self._matrix = torch.zeros((self.world, self.world), dtype=torch.int64, device=dev)
+            self._seg_start = torch.zeros(self.world, dtype=torch.int32, device=dev)
+            self._dst_base = torch.zeros(self.world, dtype=torch.int64, device=dev)
+            self._recv_pairs = torch.zeros(1, dtype=torch.int32, device=dev)
 
     @property
     def recv_rows(self) -> int:
         """Rows this rank received in the last call (reads the device count of the fused form: synchronises)."""
         return int(self._recv_rows.item()) if self._recv_rows is not None else self.last_recv_rows
 
-    def experts_on_rows(self, codes, scales, local_expert, weight, n, row_rank=None, row_pair=None):
+    def experts_on_rows(self, codes, scales, local_expert, weight, n, row_rank=None, row_pair=None, live=None):
         """The grouped GEMMs on rows that arrived from any rank: row r < n -> bf16 [6144] = (h_r @ W2[e_r]^T) * weight_r.
-        The buffers hold a multiple of four rows (rows beyond n carry expert id -1 and are dropped by the sort)."""
+        The buffers hold a multiple of four rows; rows beyond n carry expert id -1, or ``live`` (a device int32 scalar)
+        says how many rows count: either way the sort drops the rest."""
         from . import chain
         groups = codes.shape[0] // TOPK  # rows are handed to the sort as pseudo-tokens of four pairs
         if n == 0:
             return torch.empty((0, H), dtype=torch.bfloat16, device=codes.device)
         bm = chain.variant_for(groups)
-        sort = chain.moe_sort(local_expert.view(groups, TOPK), weight.view(groups, TOPK), bm, self.w.num_experts)
+        sort = chain.moe_sort(local_expert.view(groups, TOPK), weight.view(groups, TOPK), bm, self.w.num_experts,
+                              live_pairs=live)
         xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
         hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
         if row_rank is not None:
@@ -236,32 +244,27 @@ class ExpertParallelMoe:
         from . import chain
         from ... import _lib
         tokens, dev, peer = x.shape[0], x.device, self.peer
-        dest, _ = expert_owner(ids, self.world, self.experts, self.placement)
-        send = chain.moe_sort(dest.int().contiguous(), wt, 1, self.world)     # send order: pairs grouped by rank
-        counts = (dest.reshape(-1, 1) == self._ranks).sum(0)                  # rows to every rank (no host read)
-        matrix = torch.empty((self.world, self.world), dtype=counts.dtype, device=dev)
-        dist.all_gather_into_tensor(matrix, counts, group=self.group)         # matrix[s][d]: rows from rank s to rank d
-        mine = matrix[self.rank]
-        seg_start = (torch.cumsum(mine, 0) - mine).int()                      # first send row for every destination
-        dst_base = matrix[:self.rank].sum(0)                                  # where this rank's segment starts there
-        n = matrix[:, self.rank].sum()                                        # rows this rank receives (device scalar)
-        self._recv_rows = n
-        _lib.check(_lib.load().b200moe_quant_push(
-            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(send.sorted_ids.data_ptr()),
-            ctypes.c_void_p(send.sorted_weights.data_ptr()), ctypes.c_void_p(send.block_expert.data_ptr()), tokens,
+        lib, st = _lib.load(), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        dest = self._dest[:tokens * TOPK]
+        _lib.check(lib.b200moe_ep_dest(p(ids), tokens, self.world, self.experts // self.world,
+                                       int(self.placement == "interleaved"), p(dest), p(self._counts), st), "ep_dest")
+        send = chain.moe_sort(dest.view(tokens, TOPK), wt, 1, self.world)       # send order: pairs grouped by rank
+        dist.all_gather_into_tensor(self._matrix, self._counts, group=self.group)  # matrix[s][d]: rows from rank s to rank d
+        _lib.check(lib.b200moe_ep_offsets(p(self._matrix), self.world, self.rank, p(self._seg_start), p(self._dst_base),
+                                          p(self._recv_pairs), st), "ep_offsets")
+        self._recv_rows = self._recv_pairs
+        _lib.check(lib.b200moe_quant_push(
+            p(x), p(ids), p(send.sorted_ids), p(send.sorted_weights), p(send.block_expert), tokens,
             self.world, self.rank, self.experts // self.world, int(self.placement == "interleaved"), peer.ptrs["codes"],
-            peer.ptrs["scales"], peer.ptrs["meta"], ctypes.c_void_p(dst_base.data_ptr()),
-            ctypes.c_void_p(seg_start.data_ptr()), peer.capacity,
-            ctypes.c_void_p(chain.status_word(dev).data_ptr()),
-            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "quant_push")
+            peer.ptrs["scales"], peer.ptrs["meta"], p(self._dst_base), p(self._seg_start), peer.capacity,
+            p(chain.status_word(dev)), st), "quant_push")
         dist.all_reduce(self._fence, group=self.group)                        # every rank's rows have landed
-        # the receive buffers are used at their full capacity: rows from n on (left over from earlier steps) get expert
-        # id -1 and are dropped by the sort, so the number of rows that arrived never has to reach the host
-        meta = peer.local["meta"]
-        cols = meta.t().contiguous()                                          # expert, weight bits, source pair, source rank
-        cols[0].masked_fill_(self._rows >= n, -1)
+        # the receive buffers are used at their full capacity: the sort takes the number of rows that arrived from the
+        # device, so it never has to reach the host; meta is four column arrays: expert, weight bits, source pair, rank
+        cols = peer.local["meta"]
         self.experts_on_rows(peer.local["codes"], peer.local["scales"], cols[0], cols[1].view(torch.float32),
-                             peer.capacity, cols[3], cols[2])
+                             peer.capacity, cols[3], cols[2], live=self._recv_pairs)
         dist.all_reduce(self._fence, group=self.group)                        # every rank's result rows have landed
         slots = peer.local["slots"][:tokens * TOPK].view(tokens, TOPK, H)
         return slots.clone() if return_partials else chain.reduce_slots(slots)

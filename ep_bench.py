@@ -121,14 +121,45 @@ def measure(args, rank, world, local, tokens_global, zipf):
         skew = -2.2 * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))
         lgs = [lg + skew for lg in lgs]
     parity_ok, parity_bad = check_parity(layer, w_all, xs, lgs)
-    if rank != 0:
-        del w_all
+    w_all_check = w_all
     flush = L2Flush(torch)
     hx = [t.cpu().pin_memory() for t in xs]
     hl = [t.cpu().pin_memory() for t in lgs]
     hout = torch.empty((t_loc, H), dtype=torch.bfloat16).pin_memory()
 
+    # The step as CUDA-graph replays (one graph per rotating input, collectives included) when the fused form is in use:
+    # it reads nothing on the host, so it can be captured; otherwise (NCCL form, or capture unavailable) eager calls.
+    graphs, graph_outs = [], []
+    want_graph = layer.peer is not None and os.environ.get("B200MOE_EP_GRAPH", "1") == "1"
+    if want_graph:
+        ok = torch.ones(1, device="cuda")
+        try:
+            with torch.inference_mode():
+                layer.forward(xs[0], lgs[0])
+                torch.cuda.synchronize()
+                dist.barrier()
+                for i in range(N_INPUTS):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        graph_outs.append(layer.forward(xs[i], lgs[i]))
+                    graphs.append(g)
+        except Exception:  # noqa: BLE001 - any capture failure: every rank falls back to eager calls
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if not bool(ok.item()):
+            graphs = []
+    if graphs:  # a replayed step must still be the single-GPU layer's bits
+        graphs[0].replay()
+        with torch.inference_mode():
+            same = torch.equal(graph_outs[0], chain.mxfp4_moe(xs[0], w_all_check, router_logits=lgs[0])) if w_all_check is not None else True
+        flag = torch.tensor([0 if same else 1], device="cuda")
+        dist.all_reduce(flag)
+        parity_ok = parity_ok and int(flag.item()) == 0
+
     def step(i):
+        if graphs:
+            graphs[i % N_INPUTS].replay()
+            return graph_outs[i % N_INPUTS]
         return layer.forward(xs[i % N_INPUTS], lgs[i % N_INPUTS])
 
     def e2e_step(i):
@@ -164,6 +195,8 @@ def measure(args, rank, world, local, tokens_global, zipf):
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         return mx[0].item(), mx[1].item(), mx[2].item(), sm[3].item() / world
 
+    if rank != 0:
+        del w_all, w_all_check
     clocks = ClockSampler(local)
     with clocks:
         total_ms, wall_ms, max_rows, mean_rows = timed(step, args.steps, args.warmup)
@@ -185,7 +218,8 @@ def measure(args, rank, world, local, tokens_global, zipf):
                     "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
                     else "NCCL all-to-all of bf16 slot rows",
                     "max_rows_received_by_a_rank": max_rows, "mean_rows_received_per_rank": mean_rows,
-                    "timing": "CUDA events per step on every rank after the untimed L2 flush, max over ranks"})
+                    "timing": ("CUDA-graph replay of the whole step (collectives included)" if graphs else "eager calls")
+                    + ", CUDA events per step on every rank after the untimed L2 flush, max over ranks"})
         line = {"metric": "moe_layer_tokens_per_s", "value": tokens_global / (per_step * 1e-3), "unit": "tokens/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4", "data": "synthetic",

@@ -116,6 +116,13 @@ size_t b200moe_permute_scratch_bytes(int64_t tokens, int num_experts);
 int b200moe_permute(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm, int32_t* sorted_ids,
                     float* sorted_w, int32_t* block_expert, int32_t* num_valid, int32_t* scratch, void* stream);
 
+/* b200moe_permute over the first *live_pairs pairs only (a device int32; null = all 4*tokens): pairs from there on are
+ * ignored whatever their expert id. For buffers that are sorted at their full capacity while the number of filled rows is
+ * known on the device only (the expert-parallel receive buffers). No counterpart in the reference. */
+int b200moe_permute_live(const int32_t* ids, const float* w, int64_t tokens, int num_experts, int bm,
+                         const int32_t* live_pairs, int32_t* sorted_ids, float* sorted_w, int32_t* block_expert,
+                         int32_t* num_valid, int32_t* scratch, void* stream);
+
 /* The routing sort for callers that cannot allocate device memory (no counterpart in the reference, whose hosts allocate
  * every scratch buffer with torch.empty). Same inputs, outputs and results as b200moe_permute, but the chunk-count scratch
  * is a 16 KB array inside the library image instead of a caller buffer; the call performs no cudaMalloc / cudaFree and
@@ -163,14 +170,24 @@ int b200moe_dispatch_rows(const uint8_t* codes, const uint8_t* scales, const int
 int b200moe_quant_dispatch(const void* x_bf16, const int32_t* sorted_ids, const int32_t* num_valid, int64_t tokens,
                            int bm, int64_t max_rows, uint8_t* xq_sorted, uint8_t* sfx, int32_t* done, void* stream);
 
+/* Expert-parallel send plan on the device (no counterpart in the reference, which has no expert parallelism).
+ * b200moe_ep_dest: ids int32 [T][4] -> dest int32 [4T] (the rank that owns each pair's expert: id / experts_per_rank, or
+ * id % world when interleaved) and counts int64 [world] (pairs per destination). After the ranks exchanged their counts,
+ * b200moe_ep_offsets turns matrix int64 [world][world] (matrix[s][d] = pairs from s to d) into this rank's seg_start int32
+ * [world], dst_base int64 [world] (the arguments of b200moe_quant_push) and recv_pairs int32 [1] (the pairs it receives). */
+int b200moe_ep_dest(const int32_t* ids, int64_t tokens, int world, int experts_per_rank, int interleaved, int32_t* dest,
+                    int64_t* counts, void* stream);
+int b200moe_ep_offsets(const int64_t* matrix, int world, int rank, int32_t* seg_start, int64_t* dst_base,
+                       int32_t* recv_pairs, void* stream);
+
 /* Expert-parallel dispatch fused with the activation quantisation (no counterpart in the reference; its multi-GPU input
  * hand-off is the all-gather of prepared inputs, MOE/prepared_input.py:116-209). send_ids / send_w / send_rank describe
  * this rank's 4T pairs grouped by destination rank (b200moe_permute on the destination ranks with bm = 1: sorted_ids,
  * sorted_w, block_expert). Send row i goes to row dst_base[d] + (i - seg_start[d]) of destination d's receive buffers
  * (dst_base int64 [world] and seg_start int32 [world] are DEVICE arrays, so the row counts never have to reach the host):
  * peer_codes[d] u8 [capacity][3072], peer_scales[d] u8 [capacity][192] (row-major, bit-identical to b200moe_quant_mxfp4
- * of the token's row), peer_meta[d] int32 [capacity][4] = {expert id local to d, routing-weight bits, source pair
- * 4*token+slot, source rank}. Pointers are device pointers valid on this GPU (peer mappings over NVLink; this rank's own
+ * of the token's row), peer_meta[d] int32 [4][capacity] = column arrays of {expert id local to d, routing-weight
+ * bits, source pair 4*token+slot, source rank}. Pointers are device pointers valid on this GPU (peer mappings over NVLink; this rank's own
  * buffers at index `rank`); world <= 8. Rows outside [0, capacity) are not stored and set status = B200MOE_DEV_BAD_INDEX. */
 int b200moe_quant_push(const void* x_bf16, const int32_t* ids, const int32_t* send_ids, const float* send_w,
                        const int32_t* send_rank, int64_t tokens, int world, int rank, int experts_per_rank,
@@ -190,7 +207,12 @@ int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8
  * (two row blocks of one expert) x 256 weight rows (two W13 tiles), each CTA staging its own half of both operands, so
  * shared memory moves half the bytes per flop (the role of the reference's persistent prefill kernel at its widest tile,
  * MOE/gemm1_prefill_h6144_i768.py:560-598 K-loop, :689-768 epilogue). Same inputs, outputs and bits as
- * b200moe_gemm1_swiglu_quant with bm = 128. b200moe_gemm1_pair_supported(): 1 when the current device can launch it. */
+ * b200moe_gemm1_swiglu_quant with bm = 128. b200moe_gemm1_pair_supported(): 1 when the current device can launch it.
+ * b200moe_gemm1_swiglu_quant_wide: the same 256-column unit on one CTA (128 token rows x 256 weight rows per MMA, every
+ * row block a unit), same bits again. */
+int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
+                                    const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,
+                                    uint8_t* sfh, int32_t* status, void* stream);
 int b200moe_gemm1_pair_supported(void);
 int b200moe_gemm1_swiglu_quant_pair(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
                                     const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,

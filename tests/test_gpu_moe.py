@@ -80,7 +80,7 @@ def test_tensor_core_gemms_equal_cuda_core_gemms(C, tokens, bm, kind):
 @pytest.mark.parametrize("tokens,kind", [(300, "uniform"), (2048, "uniform"), (3000, "hot"), (700, "one"), (5, "dup")])
 def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
     """GEMM1 on CTA pairs (tcgen05.mma.cta_group::2, two row blocks of an expert x two W13 tiles per unit, odd last blocks
-    alone) writes the h codes and scales of the one-CTA kernel bit for bit: experts with one, an even and an odd number of
+    alone) and GEMM1 with 256 weight rows per MMA on one CTA write the h codes and scales of the 128 x 128 kernel bit for bit: experts with one, an even and an odd number of
     128-row blocks, and one expert holding every row."""
     from amd_kernels_b200 import _lib
     if not _lib.load().b200moe_gemm1_pair_supported():
@@ -101,6 +101,12 @@ def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
     sa, sp = (atoms_to_rowmajor(t.cpu().numpy(), 128)[:nv][live.cpu().numpy()] for t in (a_s, b_s))
     assert np.array_equal(sa, sp)
     assert torch.equal(b_h[:nv], C.grouped_gemm1_pair(xq, sfx, sb, w)[0][:nv])
+    # the same 256-column unit on one CTA (128 token rows x 256 weight rows per MMA)
+    c_h, c_s = C.grouped_gemm1_wide(xq, sfx, sb, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert torch.equal(a_h[:nv][live], c_h[:nv][live])
+    assert np.array_equal(sa, atoms_to_rowmajor(c_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
 
 
 def test_config0_against_reference_golden(C, layer):
