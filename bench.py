@@ -332,7 +332,15 @@ def gemm_times(torch, chain, w, layer, flush, args):
     hq, sfh = chain.grouped_gemm1(xs, sfx, sb, w)
     g2 = time_steps(torch, lambda i: chain.grouped_gemm2(hq, sfh, sb, w, slots=layer.slots), args.steps, args.warmup, flush)
     return {"g1_ms": sum(g1) / len(g1), "g2_ms": sum(g2) / len(g2), "rows": int(sb.num_valid[0]), "bm": sb.bm,
+            "rows_bound": sb.max_rows,
             "experts": int(ids.unique().numel())}
+
+
+def gemm1_kernel_name(k):
+    """The GEMM1 kernel the library selects for this many sorted rows."""
+    if k["bm"] == 128 and k["rows_bound"] >= 20000:
+        return "gemm1_wide_kernel (GEMM1, 256 weight rows per MMA, + SwiGLU-OAI + MXFP4 requantisation)"
+    return f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)"
 
 
 def gemm1_hbm_roofline(tokens, k, peaks):
@@ -341,7 +349,7 @@ def gemm1_hbm_roofline(tokens, k, peaks):
     byts = k["experts"] * W13_BYTES + k["rows"] * (H // 2 + H // 32) + k["rows"] * (I // 2 + I // 32)
     gbs = byts / (k["g1_ms"] * 1e-3) / 1e9
     g2_bytes = k["experts"] * (EXPERT_BYTES - W13_BYTES) + k["rows"] * 408 + tokens * 4 * H * 2
-    return {"kernel": f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)", "tokens": tokens,
+    return {"kernel": gemm1_kernel_name(k), "tokens": tokens,
             "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
             "peak_source": peaks["source"] + " (STREAM-style copy)", "algorithmic_bytes": byts,
             "us_per_launch": k["g1_ms"] * 1e3, "traffic": ncu_traffic(tokens),
@@ -356,7 +364,7 @@ def gemm1_tensor_roofline(tokens, k, peaks):
     tf = flops / (k["g1_ms"] * 1e-3) / 1e12
     peak = 4 * peaks["bf16_tflops"]
     g2_tf = 4 * tokens * 2 * I * H / (k["g2_ms"] * 1e-3) / 1e12
-    return {"kernel": f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)", "tokens": tokens,
+    return {"kernel": gemm1_kernel_name(k), "tokens": tokens,
             "bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
             "peak_source": "4 x " + peaks["source"] + " dense bf16 (burst), the nominal FP4:bf16 ratio",
             "algorithmic_flops": flops, "sorted_rows_incl_padding": k["rows"], "us_per_launch": k["g1_ms"] * 1e3,
