@@ -25,7 +25,7 @@
 namespace b200moe {
 
 // ------------------------------------------------------------------------------------------------ kernel
-template <int MODE, int BM, bool DUAL = false>
+template <int MODE, int BM>
 struct Cfg {
   static constexpr int kTilesM = MODE == 1 ? kW13Tiles : kW2Tiles;
   static constexpr int kTilesK = MODE == 1 ? kK1Tiles : kK2Tiles;
@@ -39,23 +39,17 @@ struct Cfg {
   // bm = 128 (prefill): the token block is the 128-row M operand and the weight tile is N, so a TMEM lane is a token and
   // the epilogue works on registers alone. Smaller blocks: the weight tile is M and the tokens are N (any multiple of 16).
   static constexpr bool kTokensAreM = BM == 128;
-  // DUAL (GEMM1 at bm = 128, many rows): the kernel is then bound by what its issuing threads can issue, so it runs TWO
-  // CTAs per SM, each with half the pipeline (3 stages), one accumulator buffer and one epilogue group: two independent
-  // instruction streams feed the tensor pipe, and one CTA's epilogue overlaps the other's MMAs. With fewer rows the
-  // kernel is bound by the weight read and the single CTA with its deeper pipeline is a little faster.
-  static_assert(!DUAL || (MODE == 1 && BM == 128), "two CTAs per SM: GEMM1 at 128-row blocks only");
-  static constexpr int kCtasPerSm = DUAL ? 2 : 1;
-  static constexpr int kAccBufs = kCtasPerSm == 2 ? 1 : 2;
-  static constexpr int kStages = BM == 128 ? (MODE == 1 ? (DUAL ? 3 : 6) : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
+  static constexpr int kAccBufs = 2;
+  static constexpr int kStages = BM == 128 ? (MODE == 1 ? 6 : 5) : (MODE == 1 && BM == 64 ? 6 : 8);
   // bm = 128 GEMM2 runs two epilogue groups of four warps, one per TMEM accumulator buffer, on alternate units
-  static constexpr int kEpiGroups = (kTokensAreM && kAccBufs == 2) ? 2 : 1;
+  static constexpr int kEpiGroups = kTokensAreM ? 2 : 1;
   // warps: 0 = copy producer, 1 = MMA issue, 2 .. = epilogue groups, last = scale-copy issue
   static constexpr int kThreads = 64 + 128 * kEpiGroups + 32;
   static constexpr int kScaleWarp = 2 + 4 * kEpiGroups;
   static constexpr int kAccCols = BM;  // fp32 accumulator columns per buffer
   // scale columns behind the accumulators: kSfSets sets of (8 for the weight tile + 8 for the token tile), used in
   // rotation: the scale copies are issued by their own thread, stages ahead of the MMAs that read them
-  static constexpr int kSfSets = kCtasPerSm == 2 ? 4 : 8;  // >= kStages: a set is reused only after its MMAs completed
+  static constexpr int kSfSets = 8;  // >= kStages: a set is reused only after its MMAs completed
   static_assert(kSfSets >= kStages, "scale sets");
   static constexpr int kSfaCol = kAccBufs * kAccCols;
   static constexpr int kSfbCol = kSfaCol + 8;
@@ -144,13 +138,13 @@ __device__ __forceinline__ RowPlacer make_placer(const EpilogueArgs& ep, __nv_bf
   return p;
 }
 
-template <int MODE, int BM, bool DUAL = false>
-__global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM, DUAL>::kCtasPerSm))
+template <int MODE, int BM>
+__global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_tiles,
                         const uint8_t* __restrict__ sf_x, const int32_t* __restrict__ block_expert,
                         const int32_t* __restrict__ num_valid, EpilogueArgs ep, int32_t* status, int num_experts,
                         int max_blocks) {
-  using C = Cfg<MODE, BM, DUAL>;
+  using C = Cfg<MODE, BM>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
@@ -280,7 +274,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
       uint32_t lo = tiles >> 4, full = sf0, empty = empty0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
-        const uint32_t acc = ui % C::kAccBufs, aph = (ui / C::kAccBufs) & 1u;
+        const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, abort_v, status)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::kAccCols;
@@ -357,7 +351,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM, DUAL>::kThreads), (Cfg<MODE, BM
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       if (C::kEpiGroups == 2 && static_cast<int>(ui & 1u) != group) continue;  // group g owns accumulator buffer g
       const int b = u / C::kTilesM, mt = u % C::kTilesM;
-      const uint32_t acc = ui % C::kAccBufs, aph = (ui / C::kAccBufs) & 1u;
+      const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
       __nv_bfloat16* my_dst = nullptr;
       float my_wt = 0.0f;
@@ -949,30 +943,22 @@ __global__ void __launch_bounds__(256, 1)
 
 // ------------------------------------------------------------------------------------------------ host side
 constexpr int64_t kWideFromRows = 20000;  // sorted rows (about 3000 tokens) from which GEMM1 uses 256 weight rows per MMA
-constexpr int64_t kDualFromRows = 36000;  // sorted rows from which the 128-column GEMM1 runs two CTAs per SM
-template <int MODE, int BM, bool DUAL = false>
+template <int MODE, int BM>
 static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* sf_x,
                   const int32_t* block_expert, const int32_t* num_valid, const EpilogueArgs& ep, int64_t max_rows,
                   int num_experts, int32_t* status, cudaStream_t stream) {
-  using C = Cfg<MODE, BM, DUAL>;
+  using C = Cfg<MODE, BM>;
   static PerDeviceOnce once;
   const int rc = once.run([] {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    if (C::kCtasPerSm > 1) {  // two CTAs need the whole shared-memory carve-out of the SM
-      e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM, DUAL>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                               cudaSharedmemCarveoutMaxShared);
-      if (e != cudaSuccess) return static_cast<int>(e);
-    }
-    return 0;
+    return static_cast<int>(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 C::kSmemBytes));
   });
   if (rc) return rc;
   const int64_t max_units = max_rows / BM * C::kTilesM;
-  const int64_t ctas = static_cast<int64_t>(sm_count()) * C::kCtasPerSm;
+  const int64_t ctas = sm_count();
   const int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
   if (grid <= 0) return 0;
-  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM, DUAL>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
+  B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
 }
 
@@ -985,10 +971,6 @@ static int launch_bm(int bm, const CUtensorMap& mx, const uint8_t* w_tiles, cons
     case 32: return launch<MODE, 32>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
     case 64: return launch<MODE, 64>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
     case 128:
-      // two CTAs per SM from ~5000 tokens' worth of sorted rows on (measured: 8192 tokens 210 -> 190 us, 2048 tokens
-      // 126 -> 129 us)
-      if (MODE == 1 && max_rows >= kDualFromRows)
-        return launch<1, 128, true>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
       return launch<MODE, 128>(mx, w_tiles, sf_x, block_expert, num_valid, ep, max_rows, num_experts, status, stream);
   }
   return B200MOE_E_ARG;
