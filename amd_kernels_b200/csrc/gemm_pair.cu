@@ -280,7 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1
         for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
           if (!mbar_wait(smem_u32(&bar_sf[s]), ph, abort_v, status)) { ok = false; break; }
-          tc_fence_after();
+          tc_fence_after();  // rows written by plain copies
           const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
           const uint32_t x_lo = lo + (C::kTokOff >> 4), w_lo = lo + (C::kWOff >> 4);
           const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
@@ -410,13 +410,45 @@ __device__ __forceinline__ void tc_mma_mxf4_wide(uint32_t d, uint32_t a_lo, uint
       : "memory");
 }
 
-__global__ void __launch_bounds__(WideCfg::kThreads, 1)
+// Token rows in their unsorted, row-major quantised form (what the row quantiser writes) plus the sorted (token, slot)
+// list: with these the kernel gathers its 128 token rows itself and no sorted copy of the activations exists.
+struct GatherRows {
+  const uint8_t* codes;       // [tokens][kH / 2]
+  const uint8_t* scales;      // [tokens][kH / 32]
+  const int32_t* sorted_ids;  // token | slot << 24; a token index >= tokens marks a padding row
+  int64_t tokens;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// GATHER false (12 warps): the token rows arrive sorted (map_x, map_sfx) and warp 0 fetches everything by TMA.
+// GATHER true (16 warps): warp 0 fetches the weights by TMA and warps 4..7 fetch the block's 128 token rows from the
+// row-major quantised tokens through the sorted list, 32 rows each, with 16-byte asynchronous copies written in the
+// 128-byte swizzle (a padding row is zero-filled) and the scale bytes into their atom cells. The eight warps that only
+// issue copies and MMAs hand registers to the eight epilogue warps (setmaxnreg), which hold a whole accumulator row.
+template <bool GATHER>
+struct WideRoles {
+  static constexpr int kThreads = GATHER ? 512 : WideCfg::kThreads;
+  static constexpr int kScaleA = 2, kScaleB = GATHER ? 3 : 11;
+  static constexpr int kGather0 = 4;                 // gather warps 4..7 (GATHER only)
+  static constexpr int kEpilogue0 = GATHER ? 8 : 3;  // eight epilogue warps from here
+  static constexpr uint32_t kFullCount = GATHER ? 1 + 128 : 1;  // the TMA arrival + one per gathering lane
+};
+
+template <bool GATHER>
+__global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
     gemm1_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_sfx,
                       const __grid_constant__ CUtensorMap map_wc, const __grid_constant__ CUtensorMap map_ws,
-                      const int32_t* __restrict__ block_expert, const int32_t* __restrict__ num_valid,
-                      uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh, int32_t* status, int num_experts,
-                      int max_blocks) {
+                      const GatherRows rows, const int32_t* __restrict__ block_expert,
+                      const int32_t* __restrict__ num_valid, uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh,
+                      int32_t* status, int num_experts, int max_blocks) {
   using C = WideCfg;
+  using R = WideRoles<GATHER>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];
   __shared__ __align__(8) uint64_t bar_empty[C::kStages];
@@ -434,7 +466,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), R::kFullCount);
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_sf[s]), 2);  // the two scale-copy threads
     }
@@ -466,8 +498,13 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
   }
   const int total = n_blocks * C::kTilePairs, stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
 
+  // GATHER: 16 warps x 128 registers at launch; warps 0..7 (two whole warpgroups, all of them only issue copies and MMAs)
+  // drop to 64 and warps 8..15 (the epilogue) rise to 192. The two sides do not meet again before the kernel's last lines.
+  const bool is_epilogue = warp >= R::kEpilogue0 && warp < R::kEpilogue0 + 8;
+  if (!is_epilogue) {
+  if (GATHER) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
-    // ---------------------------------------------------------------- producer
+    // ---------------------------------------------------------------- producer (TMA)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -484,17 +521,57 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]), base = tiles + s * C::kStageBytes;
-          mbar_arrive_expect_tx(full, C::kTx);
+          mbar_arrive_expect_tx(full, GATHER ? 2 * 128 * 128 + 4 * kAtomBytes : C::kTx);
           tma_load_2d(base + C::kWOff, &map_wc, 0, rec_lo + kt * 136, full);
           tma_load_2d(base + C::kWOff + 128 * 128, &map_wc, 0, rec_hi + kt * 136, full);
-          tma_load_2d(base + C::kTokOff, &map_x, kt * 128, b * 128, full);
+          if (!GATHER) tma_load_2d(base + C::kTokOff, &map_x, kt * 128, b * 128, full);
           tma_load_2d(base + C::kSfWLoOff, &map_ws, 0, rec_lo + kt * 136 + 128, full);
           tma_load_2d(base + C::kSfWHiOff, &map_ws, 0, rec_hi + kt * 136 + 128, full);
-          tma_load_2d(base + C::kSfTokOff, &map_sfx, 0, (b * (kH / 128) + 2 * kt) * 4, full);
+          if (!GATHER) tma_load_2d(base + C::kSfTokOff, &map_sfx, 0, (b * (kH / 128) + 2 * kt) * 4, full);
         }
       }
       if (!ok) drain_copies(bar_full, it, C::kStages);
     }
+  } else if (GATHER && warp >= R::kGather0 && warp < R::kGather0 + 4) {
+    // ---------------------------------------------------------------- token gather: this warp's 32 rows of each block
+    const int32_t* sorted_ids = rows.sorted_ids;
+    launder(sorted_ids);
+    const int gw = warp - R::kGather0;
+    const int c = lane & 7, sub = lane >> 3;  // 8 lanes x 16 bytes = one 128-byte row slice, 4 rows per instruction
+    // rows 32 gw + 4 i + sub: (row & 7) = 4 (i & 1) + sub, so a lane has two destination patterns
+    const uint32_t dst_even = static_cast<uint32_t>(C::kTokOff + (32 * gw + sub) * 128 + ((c ^ sub) << 4));
+    const uint32_t dst_odd = static_cast<uint32_t>(C::kTokOff + (32 * gw + sub) * 128 + ((c ^ (4 + sub)) << 4));
+    const uint32_t dst_sf = static_cast<uint32_t>(C::kSfTokOff + lane * 16 + gw * 4);  // atom cell of row 32 gw + lane
+    uint32_t it = 0;
+    bool ok = true;
+    int ahead = first < total ? __ldcg(sorted_ids + (first / C::kTilePairs) * 128 + 32 * gw + lane) : -1;
+    for (int u = first; u < total && ok; u += stride) {
+      const uint32_t tok = static_cast<uint32_t>(ahead) & 0x00ffffffu;
+      const uint32_t mine = tok < rows.tokens ? tok : 0xffffffffu;  // the token of row 32 gw + lane, ~0: padding
+      if (u + stride < total) ahead = __ldcg(sorted_ids + ((u + stride) / C::kTilePairs) * 128 + 32 * gw + lane);
+      const uint8_t* src[8];
+      uint32_t bytes[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t t = __shfl_sync(0xffffffffu, mine, 4 * i + sub);
+        bytes[i] = t != 0xffffffffu ? 16u : 0u;
+        src[i] = rows.codes + (t != 0xffffffffu ? static_cast<size_t>(t) * (kH / 2) : 0) + c * 16;
+      }
+      const uint8_t* ssrc = rows.scales + (mine != 0xffffffffu ? static_cast<size_t>(mine) * (kH / 32) : 0);
+      const uint32_t sbytes = mine != 0xffffffffu ? 4u : 0u;
+      for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+        const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status))) { ok = false; break; }
+        const uint32_t base = tiles + s * C::kStageBytes;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          cp_async_16(base + i * 512 + ((i & 1) ? dst_odd : dst_even), src[i] + kt * 128, bytes[i]);
+        cp_async_4(base + dst_sf, ssrc + kt * 8, sbytes);
+        cp_async_4(base + dst_sf + kAtomBytes, ssrc + kt * 8 + 4, sbytes);
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
@@ -511,6 +588,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
           if (!mbar_wait(smem_u32(&bar_sf[s]), ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
+          if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // rows written by plain copies
           const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
           const uint32_t x_lo = lo + (C::kTokOff >> 4), w_lo = lo + (C::kWOff >> 4);
           const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
@@ -524,10 +602,10 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
       }
       if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
     }
-  } else if (warp == 2 || warp == 11) {
+  } else if (warp == R::kScaleA || warp == R::kScaleB) {
     // ---------------------------------------------------------------- scale copies (three of the six atoms each)
     if (lane == 0) {
-      const bool head = warp == 2;
+      const bool head = warp == R::kScaleA;
       uint32_t it = 0;
       bool ok = true;
       for (int u = first; u < total && ok; u += stride) {
@@ -535,6 +613,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
           tc_fence_after();
+          if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
           const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
           if (head) {
@@ -551,10 +630,12 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
       }
       if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
     }
+  }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 3..10)
+    // ---------------------------------------------------------------- epilogue (eight warps)
+    if (GATHER) asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     const int q = warp & 3;
-    const int half = ((warp - 3) >> 2) & 1;
+    const int half = ((warp - R::kEpilogue0) >> 2) & 1;
     const int tr = q * 32 + lane;
     uint32_t ui = 0;
     for (int u = first; u < total; u += stride, ++ui) {
@@ -659,13 +740,45 @@ extern "C" int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_expe
   if ((r = make_flat_map(&mws, w13t, w_rows, 8))) return r;
   static PerDeviceOnce once;
   const int rc = once.run([] {
-    return static_cast<int>(cudaFuncSetAttribute(gemm1_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    return static_cast<int>(cudaFuncSetAttribute(gemm1_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   });
   if (rc) return rc;
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
-  B200MOE_LAUNCH(gemm1_wide_kernel, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc, mws,
-                 block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
+  B200MOE_LAUNCH(gemm1_wide_kernel<false>, grid, WideRoles<false>::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc,
+                 mws, GatherRows{}, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
+  return 0;
+}
+
+extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes,
+                                                 const uint8_t* scales, int64_t tokens, const int32_t* sorted_ids,
+                                                 const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows,
+                                                 uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
+  using namespace b200moe;
+  using C = WideCfg;
+  if (!w13t || !codes || !scales || !sorted_ids || !block_expert || !num_valid || !hq || !sfh || !status)
+    return B200MOE_E_ARG;
+  if (num_experts < 1 || num_experts > kMaxE || max_rows < 0 || max_rows % 128) return B200MOE_E_ARG;
+  if (tokens < 0 || tokens > (1 << 24) - 1) return B200MOE_E_ARG;  // a sorted entry carries the token in its low 24 bits
+  if (misaligned(w13t, 16) || misaligned(codes, 16) || misaligned(scales, 4) || misaligned(sorted_ids, 4) ||
+      misaligned(hq, 16) || misaligned(sfh, 16))
+    return B200MOE_E_ALIGN;
+  if (max_rows == 0) return 0;
+  CUtensorMap mwc, mws;
+  int r;
+  const uint64_t w_rows = static_cast<uint64_t>(num_experts) * kW13Tiles * kK1Tiles * 136;
+  if ((r = make_flat_map(&mwc, w13t, w_rows, 128))) return r;
+  if ((r = make_flat_map(&mws, w13t, w_rows, 8))) return r;
+  static PerDeviceOnce once;
+  const int rc = once.run([] {
+    return static_cast<int>(cudaFuncSetAttribute(gemm1_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  });
+  if (rc) return rc;
+  const int64_t max_units = max_rows / 128 * C::kTilePairs;
+  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  const GatherRows rows{codes, scales, sorted_ids, tokens};
+  B200MOE_LAUNCH(gemm1_wide_kernel<true>, grid, WideRoles<true>::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mwc, mwc, mwc,
+                 mws, rows, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
   return 0;
 }
 

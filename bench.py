@@ -233,8 +233,9 @@ class Layer:
 
     def launches_per_step(self):
         # up to 32 tokens: preparation (route + sort + quantise + gather), both GEMMs in one launch, reduce; above: routing,
-        # sort (plus a count pass above 256 tokens), quantise+gather (two kernels at 128-row blocks), two GEMMs, reduce
-        return 3 if self.tokens <= 32 else (6 if self.tokens <= 256 else (7 if self.tokens <= 1728 else 8))
+        # sort (plus a count pass above 256 tokens), quantise+gather (at 128-row blocks: quantise only, GEMM1 gathers),
+        # two GEMMs, reduce
+        return 3 if self.tokens <= 32 else (6 if self.tokens <= 256 else 7)
 
     def replay(self, i):
         self.graphs[i % len(self.graphs)].replay()
@@ -327,9 +328,14 @@ def gemm_times(torch, chain, w, layer, flush, args):
     """The two grouped GEMM launches of one layer call, each timed alone (CUDA events, cold clean L2 before every launch)."""
     wt, ids = chain.topk_route(layer.logits[0], None, 1.0, "softmax")
     sb = chain.moe_sort(ids, wt, chain.variant_for(layer.tokens))
-    xs, sfx = chain.dispatch_rows(chain.mxfp4_quant(layer.x[0]), sb)
-    g1 = time_steps(torch, lambda i: chain.grouped_gemm1(xs, sfx, sb, w), args.steps, args.warmup, flush)
-    hq, sfh = chain.grouped_gemm1(xs, sfx, sb, w)
+    q = chain.mxfp4_quant(layer.x[0])
+    if sb.bm == 128:  # the kernel the entry runs at this block height: it gathers its rows from the unsorted tokens
+        gemm1 = lambda: chain.grouped_gemm1_gather(q[0], q[1], sb, w)
+    else:
+        xs, sfx = chain.dispatch_rows(q, sb)
+        gemm1 = lambda: chain.grouped_gemm1(xs, sfx, sb, w)
+    g1 = time_steps(torch, lambda i: gemm1(), args.steps, args.warmup, flush)
+    hq, sfh = gemm1()
     g2 = time_steps(torch, lambda i: chain.grouped_gemm2(hq, sfh, sb, w, slots=layer.slots), args.steps, args.warmup, flush)
     return {"g1_ms": sum(g1) / len(g1), "g2_ms": sum(g2) / len(g2), "rows": int(sb.num_valid[0]), "bm": sb.bm,
             "rows_bound": sb.max_rows,
@@ -338,8 +344,8 @@ def gemm_times(torch, chain, w, layer, flush, args):
 
 def gemm1_kernel_name(k):
     """The GEMM1 kernel the library selects for this many sorted rows."""
-    if k["bm"] == 128 and k["rows_bound"] >= 20000:
-        return "gemm1_wide_kernel (GEMM1, 256 weight rows per MMA, + SwiGLU-OAI + MXFP4 requantisation)"
+    if k["bm"] == 128:
+        return "gemm1_wide_kernel<true> (GEMM1 gathering its token rows, 256 weight rows per MMA, + SwiGLU-OAI + MXFP4 requantisation)"
     return f"grouped_gemm_kernel<1,{k['bm']}> (GEMM1 + SwiGLU-OAI + MXFP4 requantisation)"
 
 

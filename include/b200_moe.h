@@ -213,6 +213,15 @@ int b200moe_gemm1_swiglu_quant(const uint8_t* w13t, int num_experts, const uint8
 int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
                                     const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,
                                     uint8_t* sfh, int32_t* status, void* stream);
+/* The 256-column GEMM1 reading UNSORTED tokens: `codes` [tokens][H/2] and `scales` [tokens][H/32] are the row-major output
+ * of b200moe_quant_mxfp4, `sorted_ids` the sorted (token | slot << 24) list of b200moe_moe_sort at block height 128. Each
+ * CTA gathers its 128 token rows itself (16-byte asynchronous copies, a padding row reads as zeros), so no sorted copy of
+ * the activations is written or read (the reference's prefill GEMM1 gathers through sorted_token_ids the same way,
+ * MOE/gemm1_prefill_h6144_i768.py:560-598). Same hq / sfh bits as the kernels above. */
+int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes, const uint8_t* scales,
+                                      int64_t tokens, const int32_t* sorted_ids, const int32_t* block_expert,
+                                      const int32_t* num_valid, int64_t max_rows, uint8_t* hq, uint8_t* sfh,
+                                      int32_t* status, void* stream);
 int b200moe_gemm1_pair_supported(void);
 int b200moe_gemm1_swiglu_quant_pair(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
                                     const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,

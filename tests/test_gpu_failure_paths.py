@@ -84,3 +84,34 @@ def test_out_of_range_routing_tables_set_the_status_and_touch_nothing_outside(C,
     after = C.grouped_gemm2(*C.grouped_gemm1(xq, sfx, sort, w), sort, w)
     torch.cuda.synchronize()
     assert C.last_status() == 0 and torch.equal(after, good)
+
+
+def test_the_gathering_gemm1_never_reads_outside_the_tokens(C, small):
+    """The GEMM1 that gathers its own rows: an expert id outside the weights is replaced and reported; a sorted entry
+    whose token index is not below the token count (whatever its bits) is a padding row and reads as zeros, so a corrupt
+    list cannot form an address outside the quantised tokens."""
+    from amd_kernels_b200 import _lib
+    w, x, wt, ids = small
+    sort = C.moe_sort(ids, wt, 128, w.num_experts)
+    q, s = C.mxfp4_quant(x)
+    xq, sfx = C.quant_dispatch(x, sort)
+    nv = int(sort.num_valid[0])
+    good = C.grouped_gemm1(xq, sfx, sort, w)[0][:nv]
+    assert torch.equal(C.grouped_gemm1_gather(q, s, sort, w)[0][:nv], good)
+    assert C.last_status() == 0
+    bad = C.SortBuffers(sort.sorted_ids, sort.sorted_weights, sort.block_expert.clone(), sort.num_valid, sort.bm, sort.tokens)
+    bad.block_expert[0] = -3
+    C.grouped_gemm1_gather(q, s, bad, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == _lib.DEV_BAD_INDEX
+    wild = sort.sorted_ids.clone()
+    wild[::3] = torch.randint(sort.tokens, 1 << 24, (wild[::3].numel(),), device="cuda", dtype=torch.int32) | (0x7F << 24)
+    wild[1::3] = -1
+    odd = C.SortBuffers(wild, sort.sorted_weights, sort.block_expert, sort.num_valid, sort.bm, sort.tokens)
+    h = C.grouped_gemm1_gather(q, s, odd, w)[0][:nv]
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    kept = torch.arange(nv, device="cuda") % 3 == 2
+    assert torch.equal(h[kept], good[kept])  # rows whose entry was left alone are unchanged
+    assert not bool(h[~kept].any())  # a padding row's h is zero (codes of 0.0)
+    assert torch.equal(C.grouped_gemm1_gather(q, s, sort, w)[0][:nv], good)

@@ -107,6 +107,14 @@ def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
     assert C.last_status() == 0
     assert torch.equal(a_h[:nv][live], c_h[:nv][live])
     assert np.array_equal(sa, atoms_to_rowmajor(c_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
+    # the same kernel gathering its rows from the unsorted row-major quantised tokens (no sorted copy of the activations)
+    q, s = C.mxfp4_quant(bf16_dev(xb))
+    d_h, d_s = C.grouped_gemm1_gather(q, s, sb, w)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert torch.equal(a_h[:nv][live], d_h[:nv][live])
+    assert np.array_equal(sa, atoms_to_rowmajor(d_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
+    assert torch.equal(d_h[:nv], C.grouped_gemm1_gather(q, s, sb, w)[0][:nv])
 
 
 def test_config0_against_reference_golden(C, layer):
