@@ -382,24 +382,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1
 // ------------------------------------------------------------------------------------------------ one CTA, N = 256
 // The same 256-column unit on ONE CTA: M = 128 token rows (one row block) x N = 256 weight rows (two W13 tiles) per
 // tcgen05.mma.cta_group::1. Every block is a unit, so an expert's odd last block costs nothing extra; the price is that the
-// CTA stages both weight tiles itself (51 KB per stage, 4 stages). Roles as in the pair kernel: warp 0 producer, warp 1
-// MMA issue (and TMEM), warps 2 and 11 the scale copies, warps 3-10 the register-only epilogue.
+// CTA stages both weight tiles itself (48 KB of codes per stage, 4 stages).
+//
+// Two rings. Measured on the one-ring form of this kernel (codes and scales of a K-tile in one stage): a stage's ring was
+// free -> 6 copies issued (~650 cycles) -> last byte landed (~1350) -> scales copied to tensor memory and seen by the MMA
+// thread (~860) -> MMAs run and seen complete (~680), 3500 cycles for 4 stages = 880 per stage against 512 of tensor time.
+// The scales are 6 % of the bytes, so they get a ring of their own, twice as deep: a dedicated warp fetches them 8 K-tiles
+// ahead and the two copy threads move them into tensor memory as soon as the stage 4 tiles back has been consumed, which
+// is long before the codes of their own tile land. The MMA thread then waits for codes only, and the scale copy has left
+// the critical ring.
+//
+//   warp 0      code producer: TMA of the two weight tiles (and, sorted input, the token tile)
+//   warp 1      tensor memory; one thread issues the MMAs
+//   warps 2, 3  one thread each: three of the six scale atoms smem -> tensor memory (tcgen05.cp), then commit
+//   warps 4-7   GATHER only: each fetches 32 token rows of the block by the sorted list (16-byte asynchronous copies)
+//   warp 8      scale producer: TMA of the weight scales (and the token scales, or GATHER: gathers them, 4 rows per lane)
+//   warps 12-19 epilogue: thread = one token row, a whole accumulator half-row in registers
+// 20 warps start with 96 registers; warps 0..11 drop to 48 and the epilogue warps rise to 168
+// (setmaxnreg; 12 x 48 + 8 x 168 = 20 x 96: the exchange must balance inside what the CTA was given at launch).
 struct WideCfg {
-  static constexpr int kStages = 4;
+  static constexpr int kStages = 4;                  // code ring
+  static constexpr int kSfStages = 8;                // scale ring = scale sets in tensor memory
   static constexpr int kTokOff = 0;
   static constexpr int kWOff = 128 * 128;            // 256 weight rows x 128 bytes: tile 2*tp, then tile 2*tp+1
-  static constexpr int kSfTokOff = 3 * 128 * 128;
-  static constexpr int kSfWLoOff = kSfTokOff + 2 * kAtomBytes;
-  static constexpr int kSfWHiOff = kSfWLoOff + 2 * kAtomBytes;
-  static constexpr int kStageBytes = kSfWHiOff + 2 * kAtomBytes;  // 52224
-  static constexpr int kThreads = PairCfg::kThreads;
-  static constexpr int kSfSets = 8;
+  static constexpr int kStageBytes = 3 * 128 * 128;  // 49152
+  static constexpr int kSfRingOff = kStages * kStageBytes;
+  static constexpr int kSfTokOff = 0;                // inside a scale slot: token atoms 0, 1
+  static constexpr int kSfWLoOff = 2 * kAtomBytes;   // tile 2*tp, K-atoms 0, 1
+  static constexpr int kSfWHiOff = 4 * kAtomBytes;   // tile 2*tp+1
+  static constexpr int kSfSlotBytes = 6 * kAtomBytes;
+  static constexpr int kThreads = 32 * 20;
+  static constexpr int kGather0 = 4, kScaleProducer = 8, kEpilogue0 = 12;
   static constexpr int kSfCol = 256;
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kSmemBytes = kSfRingOff + kSfStages * kSfSlotBytes + 1024;
   static constexpr int kTilePairs = kW13Tiles / 2;
-  static constexpr uint32_t kTx = 3 * 128 * 128 + 6 * kAtomBytes;
 };
+static_assert(WideCfg::kSfCol + 24 * WideCfg::kSfStages <= WideCfg::kTmemCols, "tensor memory columns");
+static_assert(kK1Tiles % WideCfg::kSfStages == 0, "a unit starts at slot 0 of both rings");
 
 __device__ __forceinline__ void tc_mma_mxf4_wide(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa,
                                                  uint32_t sfb, uint32_t accumulate) {
@@ -425,34 +445,25 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint3
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {  // arrives once this thread's copies so far have landed
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 
-// GATHER false (12 warps): the token rows arrive sorted (map_x, map_sfx) and warp 0 fetches everything by TMA.
-// GATHER true (16 warps): warp 0 fetches the weights by TMA and warps 4..7 fetch the block's 128 token rows from the
-// row-major quantised tokens through the sorted list, 32 rows each, with 16-byte asynchronous copies written in the
-// 128-byte swizzle (a padding row is zero-filled) and the scale bytes into their atom cells. The eight warps that only
-// issue copies and MMAs hand registers to the eight epilogue warps (setmaxnreg), which hold a whole accumulator row.
+// GATHER false: the token rows arrive sorted (map_x, map_sfx). GATHER true: rows come from `rows` through the sorted list
+// (a padding row is zero-filled), written in the 128-byte swizzle, the scale bytes into their atom cells.
 template <bool GATHER>
-struct WideRoles {
-  static constexpr int kThreads = GATHER ? 512 : WideCfg::kThreads;
-  static constexpr int kScaleA = 2, kScaleB = GATHER ? 3 : 11;
-  static constexpr int kGather0 = 4;                 // gather warps 4..7 (GATHER only)
-  static constexpr int kEpilogue0 = GATHER ? 8 : 3;  // eight epilogue warps from here
-  static constexpr uint32_t kFullCount = GATHER ? 1 + 128 : 1;  // the TMA arrival + one per gathering lane
-};
-
-template <bool GATHER>
-__global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
+__global__ void __launch_bounds__(WideCfg::kThreads, 1)
     gemm1_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_sfx,
                       const __grid_constant__ CUtensorMap map_wc, const __grid_constant__ CUtensorMap map_ws,
                       const GatherRows rows, const int32_t* __restrict__ block_expert,
                       const int32_t* __restrict__ num_valid, uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh,
                       int32_t* status, int num_experts, int max_blocks) {
   using C = WideCfg;
-  using R = WideRoles<GATHER>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[C::kStages];
-  __shared__ __align__(8) uint64_t bar_empty[C::kStages];
-  __shared__ __align__(8) uint64_t bar_sf[C::kStages];
+  __shared__ __align__(8) uint64_t bar_full[C::kStages];     // the stage's codes have landed
+  __shared__ __align__(8) uint64_t bar_empty[C::kStages];    // the MMAs that read the stage have completed
+  __shared__ __align__(8) uint64_t bar_sfull[C::kSfStages];  // the slot's scales have landed in shared memory
+  __shared__ __align__(8) uint64_t bar_sf[C::kSfStages];     // ... and have been copied to tensor memory
   __shared__ __align__(8) uint64_t bar_tfull;
   __shared__ __align__(8) uint64_t bar_tempty;
   __shared__ __align__(8) uint64_t bar_drain[2];
@@ -461,14 +472,18 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sf_ring = tiles + C::kSfRingOff;
   volatile int* abort_v = &abort_flag;
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), R::kFullCount);
+      mbar_init(smem_u32(&bar_full[s]), GATHER ? 1 + 128 : 1);  // the TMA arrival (+ one per gathering lane)
       mbar_init(smem_u32(&bar_empty[s]), 1);
-      mbar_init(smem_u32(&bar_sf[s]), 2);  // the two scale-copy threads
+    }
+    for (int j = 0; j < C::kSfStages; ++j) {
+      mbar_init(smem_u32(&bar_sfull[j]), GATHER ? 1 + 32 : 1);
+      mbar_init(smem_u32(&bar_sf[j]), 2);  // the two scale-copy threads
     }
     mbar_init(smem_u32(&bar_tfull), 1);
     mbar_init(smem_u32(&bar_tempty), 8);  // one arrival per epilogue warp
@@ -497,14 +512,14 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
     n_blocks = 0;
   }
   const int total = n_blocks * C::kTilePairs, stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
+  const int32_t* sorted_ids = rows.sorted_ids;
+  launder(sorted_ids);
 
-  // GATHER: 16 warps x 128 registers at launch; warps 0..7 (two whole warpgroups, all of them only issue copies and MMAs)
-  // drop to 64 and warps 8..15 (the epilogue) rise to 192. The two sides do not meet again before the kernel's last lines.
-  const bool is_epilogue = warp >= R::kEpilogue0 && warp < R::kEpilogue0 + 8;
-  if (!is_epilogue) {
-  if (GATHER) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  // The two register groups (three and two whole warpgroups) do not meet again before the kernel's last lines.
+  if (warp < C::kEpilogue0) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
   if (warp == 0) {
-    // ---------------------------------------------------------------- producer (TMA)
+    // ---------------------------------------------------------------- code producer (TMA)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -521,27 +536,67 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]), base = tiles + s * C::kStageBytes;
-          mbar_arrive_expect_tx(full, GATHER ? 2 * 128 * 128 + 4 * kAtomBytes : C::kTx);
+          mbar_arrive_expect_tx(full, (GATHER ? 2 : 3) * 128 * 128);
           tma_load_2d(base + C::kWOff, &map_wc, 0, rec_lo + kt * 136, full);
           tma_load_2d(base + C::kWOff + 128 * 128, &map_wc, 0, rec_hi + kt * 136, full);
           if (!GATHER) tma_load_2d(base + C::kTokOff, &map_x, kt * 128, b * 128, full);
-          tma_load_2d(base + C::kSfWLoOff, &map_ws, 0, rec_lo + kt * 136 + 128, full);
-          tma_load_2d(base + C::kSfWHiOff, &map_ws, 0, rec_hi + kt * 136 + 128, full);
-          if (!GATHER) tma_load_2d(base + C::kSfTokOff, &map_sfx, 0, (b * (kH / 128) + 2 * kt) * 4, full);
         }
       }
       if (!ok) drain_copies(bar_full, it, C::kStages);
     }
-  } else if (GATHER && warp >= R::kGather0 && warp < R::kGather0 + 4) {
+  } else if (warp == C::kScaleProducer) {
+    // ---------------------------------------------------------------- scale producer, 8 K-tiles deep
+    // GATHER: lane L owns token rows L, L + 32, L + 64, L + 96 of the block: two 4-byte cells per row and K-tile
+    const uint32_t cell = static_cast<uint32_t>(C::kSfTokOff + lane * 16);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int u = first; u < total && ok; u += stride) {
+      const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+      int e = __ldcg(block_expert + b);
+      if (e < 0 || e >= num_experts) e = 0;  // reported by the code producer
+      const int rec_lo = ((e * kW13Tiles + 2 * tp) * kK1Tiles) * 136, rec_hi = rec_lo + kK1Tiles * 136;
+      uint32_t soff[4];  // byte offset of the row's scales, ~0: a padding row
+      if (GATHER) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const uint32_t tok = static_cast<uint32_t>(__ldcg(sorted_ids + b * 128 + 32 * m + lane)) & 0x00ffffffu;
+          soff[m] = tok < rows.tokens ? tok * static_cast<uint32_t>(kH / 32) : 0xffffffffu;
+        }
+      }
+      for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
+        const uint32_t j = it % C::kSfStages, ph = (it / C::kSfStages) & 1u;
+        // the slot is free once the copy threads have moved its previous contents to tensor memory
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_sf[j]), ph ^ 1u, abort_v, status))) { ok = false; break; }
+        const uint32_t sfull = smem_u32(&bar_sfull[j]), slot = sf_ring + j * C::kSfSlotBytes;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(sfull, (GATHER ? 4 : 6) * kAtomBytes);
+          tma_load_2d(slot + C::kSfWLoOff, &map_ws, 0, rec_lo + kt * 136 + 128, sfull);
+          tma_load_2d(slot + C::kSfWHiOff, &map_ws, 0, rec_hi + kt * 136 + 128, sfull);
+          if (!GATHER) tma_load_2d(slot + C::kSfTokOff, &map_sfx, 0, (b * (kH / 128) + 2 * kt) * 4, sfull);
+        }
+        if (GATHER) {
+          __syncwarp();
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const bool live = soff[m] != 0xffffffffu;
+            const uint8_t* src = rows.scales + (live ? soff[m] : 0u) + kt * 8;
+            cp_async_4(slot + cell + m * 4, src, live ? 4u : 0u);
+            cp_async_4(slot + cell + m * 4 + kAtomBytes, src + 4, live ? 4u : 0u);
+          }
+          cp_async_arrive(sfull);
+        }
+      }
+    }
+    if (GATHER) asm volatile("cp.async.wait_all;" ::: "memory");
+    if (!ok && lane == 0) drain_copies(bar_sfull, it, C::kSfStages);
+  } else if (GATHER && warp >= C::kGather0 && warp < C::kGather0 + 4) {
     // ---------------------------------------------------------------- token gather: this warp's 32 rows of each block
-    const int32_t* sorted_ids = rows.sorted_ids;
-    launder(sorted_ids);
-    const int gw = warp - R::kGather0;
+    const int gw = warp - C::kGather0;
     const int c = lane & 7, sub = lane >> 3;  // 8 lanes x 16 bytes = one 128-byte row slice, 4 rows per instruction
     // rows 32 gw + 4 i + sub: (row & 7) = 4 (i & 1) + sub, so a lane has two destination patterns
     const uint32_t dst_even = static_cast<uint32_t>(C::kTokOff + (32 * gw + sub) * 128 + ((c ^ sub) << 4));
     const uint32_t dst_odd = static_cast<uint32_t>(C::kTokOff + (32 * gw + sub) * 128 + ((c ^ (4 + sub)) << 4));
-    const uint32_t dst_sf = static_cast<uint32_t>(C::kSfTokOff + lane * 16 + gw * 4);  // atom cell of row 32 gw + lane
+    const uint8_t* codes = rows.codes + c * 16;
     uint32_t it = 0;
     bool ok = true;
     int ahead = first < total ? __ldcg(sorted_ids + (first / C::kTilePairs) * 128 + 32 * gw + lane) : -1;
@@ -549,26 +604,23 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
       const uint32_t tok = static_cast<uint32_t>(ahead) & 0x00ffffffu;
       const uint32_t mine = tok < rows.tokens ? tok : 0xffffffffu;  // the token of row 32 gw + lane, ~0: padding
       if (u + stride < total) ahead = __ldcg(sorted_ids + ((u + stride) / C::kTilePairs) * 128 + 32 * gw + lane);
-      const uint8_t* src[8];
-      uint32_t bytes[8];
+      uint32_t off[8];  // byte offset of the row's codes (the host keeps tokens * H/2 below 2^32), ~0: padding
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const uint32_t t = __shfl_sync(0xffffffffu, mine, 4 * i + sub);
-        bytes[i] = t != 0xffffffffu ? 16u : 0u;
-        src[i] = rows.codes + (t != 0xffffffffu ? static_cast<size_t>(t) * (kH / 2) : 0) + c * 16;
+        off[i] = t != 0xffffffffu ? t * static_cast<uint32_t>(kH / 2) : 0xffffffffu;
       }
-      const uint8_t* ssrc = rows.scales + (mine != 0xffffffffu ? static_cast<size_t>(mine) * (kH / 32) : 0);
-      const uint32_t sbytes = mine != 0xffffffffu ? 4u : 0u;
       for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
         const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status))) { ok = false; break; }
         const uint32_t base = tiles + s * C::kStageBytes;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          cp_async_16(base + i * 512 + ((i & 1) ? dst_odd : dst_even), src[i] + kt * 128, bytes[i]);
-        cp_async_4(base + dst_sf, ssrc + kt * 8, sbytes);
-        cp_async_4(base + dst_sf + kAtomBytes, ssrc + kt * 8 + 4, sbytes);
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+        for (int i = 0; i < 8; ++i) {
+          const bool live = off[i] != 0xffffffffu;
+          cp_async_16(base + i * 512 + ((i & 1) ? dst_odd : dst_even), codes + (live ? off[i] : 0u) + kt * 128,
+                      live ? 16u : 0u);
+        }
+        cp_async_arrive(smem_u32(&bar_full[s]));
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -585,13 +637,15 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
         if (!mbar_wait(smem_u32(&bar_tempty), (ui & 1u) ^ 1u, abort_v, status)) break;
         tc_fence_after();
         for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
-          if (!mbar_wait(smem_u32(&bar_sf[s]), ph, abort_v, status)) { ok = false; break; }
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          const uint32_t j = it % C::kSfStages, sph = (it / C::kSfStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_sf[j]), sph, abort_v, status)) { ok = false; break; }   // long since complete
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }  // the wait that matters
           tc_fence_after();
           if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // rows written by plain copies
           const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
           const uint32_t x_lo = lo + (C::kTokOff >> 4), w_lo = lo + (C::kWOff >> 4);
-          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * j, t_sfw = t_sft + 8u;
           tc_mma_mxf4_wide(tmem_base, x_lo, w_lo, kId0, t_sft, t_sfw, static_cast<uint32_t>(kt != 0));
           tc_mma_mxf4_wide(tmem_base, x_lo + 2, w_lo + 2, kId1, t_sft, t_sfw, 1u);
           tc_mma_mxf4_wide(tmem_base, x_lo + 4, w_lo + 4, kId0, t_sft + 4, t_sfw + 8, 1u);
@@ -602,20 +656,23 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
       }
       if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[0]));
     }
-  } else if (warp == R::kScaleA || warp == R::kScaleB) {
+  } else if (warp == 2 || warp == 3) {
     // ---------------------------------------------------------------- scale copies (three of the six atoms each)
     if (lane == 0) {
-      const bool head = warp == R::kScaleA;
+      const bool head = warp == 2;
       uint32_t it = 0;
       bool ok = true;
       for (int u = first; u < total && ok; u += stride) {
         for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u, sfset = it & (C::kSfSets - 1);
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_v, status)) { ok = false; break; }
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          const uint32_t j = it % C::kSfStages, sph = (it / C::kSfStages) & 1u;
+          if (!mbar_wait(smem_u32(&bar_sfull[j]), sph, abort_v, status)) { ok = false; break; }
+          // scale set j was last read by the MMAs of K-tile it - 8: complete once those of K-tile it - 4 are
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_v, status)) { ok = false; break; }
           tc_fence_after();
           if (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          const uint32_t lo = (tiles + s * C::kStageBytes) >> 4;
-          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * sfset, t_sfw = t_sft + 8u;
+          const uint32_t lo = (sf_ring + j * C::kSfSlotBytes) >> 4;
+          const uint32_t t_sft = tmem_base + C::kSfCol + 24u * j, t_sfw = t_sft + 8u;
           if (head) {
             tc_cp_scales_lo(t_sft, lo + (C::kSfTokOff >> 4));
             tc_cp_scales_lo(t_sft + 4, lo + ((C::kSfTokOff + kAtomBytes) >> 4));
@@ -625,7 +682,7 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
             tc_cp_scales_lo(t_sfw + 8, lo + ((C::kSfWLoOff + kAtomBytes) >> 4));
             tc_cp_scales_lo(t_sfw + 12, lo + ((C::kSfWHiOff + kAtomBytes) >> 4));
           }
-          tc_commit(smem_u32(&bar_sf[s]));
+          tc_commit(smem_u32(&bar_sf[j]));
         }
       }
       if (*abort_v) drain_tcgen05(smem_u32(&bar_drain[1]));
@@ -633,9 +690,9 @@ __global__ void __launch_bounds__(WideRoles<GATHER>::kThreads, 1)
   }
   } else {
     // ---------------------------------------------------------------- epilogue (eight warps)
-    if (GATHER) asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
     const int q = warp & 3;
-    const int half = ((warp - R::kEpilogue0) >> 2) & 1;
+    const int half = ((warp - C::kEpilogue0) >> 2) & 1;
     const int tr = q * 32 + lane;
     uint32_t ui = 0;
     for (int u = first; u < total; u += stride, ++ui) {
@@ -745,7 +802,7 @@ extern "C" int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_expe
   if (rc) return rc;
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
-  B200MOE_LAUNCH(gemm1_wide_kernel<false>, grid, WideRoles<false>::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc,
+  B200MOE_LAUNCH(gemm1_wide_kernel<false>, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc,
                  mws, GatherRows{}, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
   return 0;
 }
@@ -777,7 +834,7 @@ extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_ex
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   const GatherRows rows{codes, scales, sorted_ids, tokens};
-  B200MOE_LAUNCH(gemm1_wide_kernel<true>, grid, WideRoles<true>::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mwc, mwc, mwc,
+  B200MOE_LAUNCH(gemm1_wide_kernel<true>, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mwc, mwc, mwc,
                  mws, rows, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
   return 0;
 }
