@@ -57,7 +57,7 @@ SIGNATURES = {
     "b200moe_gemm1_pair_supported": (c_int, []),
     "b200moe_gemm1_swiglu_quant_pair": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
     "b200moe_gemm1_swiglu_quant_wide": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
-    "b200moe_gemm1_swiglu_quant_gather": (c_int, [_P, c_int, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, _P]),
+    "b200moe_gemm1_swiglu_quant_gather": (c_int, [_P, c_int, _P, _P, c_int64, c_int, _P, _P, _P, c_int64, _P, _P, _P, _P]),
     "b200moe_gemm2_weighted": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_weighted_peer": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int,
                                             c_int64, _P, _P]),

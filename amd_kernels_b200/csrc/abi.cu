@@ -127,7 +127,7 @@ static int experts_gathering_and_reduce(const b200moe_weights* w, const Workspac
                                         void* out_bf16, int32_t* status, void* stream) {
   const int ne = w->num_experts;
   int r;
-  if ((r = b200moe_gemm1_swiglu_quant_gather(w->w13t, ne, ws.q4, ws.s4, tokens, ws.sorted_ids, ws.block_expert, ws.num_valid,
+  if ((r = b200moe_gemm1_swiglu_quant_gather(w->w13t, ne, ws.q4, ws.s4, tokens, 0, ws.sorted_ids, ws.block_expert, ws.num_valid,
                                              ws.rows, ws.hq, ws.sfh, status, stream)))
     return r;
   if ((r = b200moe_gemm2_weighted(w->w2t, ne, ws.hq, ws.sfh, ws.block_expert, ws.num_valid, ws.sorted_ids, ws.sorted_w,

@@ -437,7 +437,15 @@ struct GatherRows {
   const uint8_t* scales;      // [tokens][kH / 32]
   const int32_t* sorted_ids;  // token | slot << 24; a token index >= tokens marks a padding row
   int64_t tokens;
+  int by_pair;                // 1: codes / scales hold one row per (token, slot) pair, row 4 * token + slot
 };
+
+// row of the quantised input that sorted entry `sid` reads, ~0 for a padding row
+__device__ __forceinline__ uint32_t gather_row(int sid, const GatherRows& rows) {
+  const uint32_t tok = static_cast<uint32_t>(sid) & 0x00ffffffu;
+  if (tok >= rows.tokens) return 0xffffffffu;
+  return rows.by_pair ? tok * kTopK + ((static_cast<uint32_t>(sid) >> 24) & 3u) : tok;
+}
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -559,8 +567,8 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
       if (GATHER) {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-          const uint32_t tok = static_cast<uint32_t>(__ldcg(sorted_ids + b * 128 + 32 * m + lane)) & 0x00ffffffu;
-          soff[m] = tok < rows.tokens ? tok * static_cast<uint32_t>(kH / 32) : 0xffffffffu;
+          const uint32_t row = gather_row(__ldcg(sorted_ids + b * 128 + 32 * m + lane), rows);
+          soff[m] = row != 0xffffffffu ? row * static_cast<uint32_t>(kH / 32) : 0xffffffffu;
         }
       }
       for (int kt = 0; kt < kK1Tiles; ++kt, ++it) {
@@ -601,8 +609,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
     bool ok = true;
     int ahead = first < total ? __ldcg(sorted_ids + (first / C::kTilePairs) * 128 + 32 * gw + lane) : -1;
     for (int u = first; u < total && ok; u += stride) {
-      const uint32_t tok = static_cast<uint32_t>(ahead) & 0x00ffffffu;
-      const uint32_t mine = tok < rows.tokens ? tok : 0xffffffffu;  // the token of row 32 gw + lane, ~0: padding
+      const uint32_t mine = gather_row(ahead, rows);  // the input row of block row 32 gw + lane, ~0: padding
       if (u + stride < total) ahead = __ldcg(sorted_ids + ((u + stride) / C::kTilePairs) * 128 + 32 * gw + lane);
       uint32_t off[8];  // byte offset of the row's codes (the host keeps tokens * H/2 below 2^32), ~0: padding
 #pragma unroll
@@ -808,7 +815,7 @@ extern "C" int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_expe
 }
 
 extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes,
-                                                 const uint8_t* scales, int64_t tokens, const int32_t* sorted_ids,
+                                                 const uint8_t* scales, int64_t tokens, int by_pair, const int32_t* sorted_ids,
                                                  const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows,
                                                  uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
   using namespace b200moe;
@@ -833,7 +840,7 @@ extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_ex
   if (rc) return rc;
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
-  const GatherRows rows{codes, scales, sorted_ids, tokens};
+  const GatherRows rows{codes, scales, sorted_ids, tokens, by_pair ? 1 : 0};
   B200MOE_LAUNCH(gemm1_wide_kernel<true>, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mwc, mwc, mwc,
                  mws, rows, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
   return 0;

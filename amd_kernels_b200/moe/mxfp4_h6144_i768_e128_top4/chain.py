@@ -322,19 +322,20 @@ def grouped_gemm1_wide(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
     return hq, sfh
 
 
-def grouped_gemm1_gather(codes, scales, sort: SortBuffers, w: MoeWeights):
+def grouped_gemm1_gather(codes, scales, sort: SortBuffers, w: MoeWeights, by_pair: bool = False):
     """``grouped_gemm1`` at block height 128 straight from the UNSORTED row-major quantised tokens (``quant_mxfp4``'s codes
     [T, 3072] and scales [T, 192]): the kernel gathers each block's rows by ``sort.sorted_ids`` itself, the way the
     reference's prefill GEMM1 reads through sorted_token_ids (gemm1_prefill_h6144_i768.py:560-598). The same h codes and
-    scale atoms as ``quant_dispatch`` + ``grouped_gemm1``."""
+    scale atoms as ``quant_dispatch`` + ``grouped_gemm1``. ``by_pair``: the input holds one row per (token, slot) pair
+    instead of one per token (rows that arrived from other ranks)."""
     if sort.bm != 128:
         raise ValueError("the gathering GEMM1 serves block height 128")
     dev = codes.device
-    tokens = codes.shape[0]
+    tokens = sort.tokens
     hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
     sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
     _lib.check(w.lib().b200moe_gemm1_swiglu_quant_gather(_ptr(w.w13), w.num_experts, _ptr(codes), _ptr(scales), tokens,
-                                                         _ptr(sort.sorted_ids), _ptr(sort.block_expert),
+                                                         int(by_pair), _ptr(sort.sorted_ids), _ptr(sort.block_expert),
                                                          _ptr(sort.num_valid), sort.max_rows, _ptr(hq), _ptr(sfh),
                                                          _ptr(status_word(dev)), _stream(dev)),
                "gemm1_swiglu_quant_gather")

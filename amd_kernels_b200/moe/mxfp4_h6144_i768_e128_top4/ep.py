@@ -175,8 +175,11 @@ class ExpertParallelMoe:
         bm = chain.variant_for(groups)
         sort = chain.moe_sort(local_expert.view(groups, TOPK), weight.view(groups, TOPK), bm, self.w.num_experts,
                               live_pairs=live)
-        xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
-        hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
+        if bm == 128:  # GEMM1 reads the received rows through the sorted list itself: no sorted copy
+            hq, sfh = chain.grouped_gemm1_gather(codes, scales, sort, self.w, by_pair=True)
+        else:
+            xq, sfx = chain.dispatch_rows((codes, scales), sort, by_pair=True)
+            hq, sfh = chain.grouped_gemm1(xq, sfx, sort, self.w)
         if row_rank is not None:
             chain.grouped_gemm2_peer(hq, sfh, sort, self.w, row_rank, row_pair, self.peer.ptrs["slots"], self.world,
                                      self.peer.max_pairs)

@@ -217,9 +217,10 @@ int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_experts, const 
  * of b200moe_quant_mxfp4, `sorted_ids` the sorted (token | slot << 24) list of b200moe_moe_sort at block height 128. Each
  * CTA gathers its 128 token rows itself (16-byte asynchronous copies, a padding row reads as zeros), so no sorted copy of
  * the activations is written or read (the reference's prefill GEMM1 gathers through sorted_token_ids the same way,
- * MOE/gemm1_prefill_h6144_i768.py:560-598). Same hq / sfh bits as the kernels above. */
+ * MOE/gemm1_prefill_h6144_i768.py:560-598). `by_pair` != 0: codes / scales hold one row per (token, slot) pair, row
+ * 4 * token + slot (rows that arrived from other ranks). Same hq / sfh bits as the kernels above. */
 int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes, const uint8_t* scales,
-                                      int64_t tokens, const int32_t* sorted_ids, const int32_t* block_expert,
+                                      int64_t tokens, int by_pair, const int32_t* sorted_ids, const int32_t* block_expert,
                                       const int32_t* num_valid, int64_t max_rows, uint8_t* hq, uint8_t* sfh,
                                       int32_t* status, void* stream);
 int b200moe_gemm1_pair_supported(void);

@@ -115,6 +115,16 @@ def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
     assert torch.equal(a_h[:nv][live], d_h[:nv][live])
     assert np.array_equal(sa, atoms_to_rowmajor(d_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
     assert torch.equal(d_h[:nv], C.grouped_gemm1_gather(q, s, sb, w)[0][:nv])
+    # one input row per (token, slot) pair (rows that arrived from other ranks): row 4 * token + slot, all different
+    pick = (torch.arange(4 * tokens, device="cuda") * 7 + 3) % tokens
+    qp, sp_ = q[pick].contiguous(), s[pick].contiguous()
+    e_h, e_s = C.grouped_gemm1(*C.dispatch_rows((qp, sp_), sb, by_pair=True), sb, w)
+    f_h, f_s = C.grouped_gemm1_gather(qp, sp_, sb, w, by_pair=True)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert torch.equal(e_h[:nv][live], f_h[:nv][live])
+    assert np.array_equal(atoms_to_rowmajor(e_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()],
+                          atoms_to_rowmajor(f_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
 
 
 def test_config0_against_reference_golden(C, layer):
