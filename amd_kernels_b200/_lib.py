@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200moe_permute_live": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_ep_dest": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, _P, _P]),
     "b200moe_ep_offsets": (c_int, [_P, c_int, c_int, _P, _P, _P, _P]),
+    "b200moe_ep_sync": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, _P]),
     "b200moe_permute_static": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, _P, _P, _P]),
     "b200moe_route_sort": (c_int, [_P, _P, c_int64, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_dispatch_rows": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int64, _P, _P, _P]),

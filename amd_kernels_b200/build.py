@@ -15,7 +15,7 @@ SIBLING_INTERMEDIATES = (1536,)  # further builds of the same sources: libb200mo
 def lib_path(inter: int = 768) -> str:
     return LIB if inter == 768 else os.path.join(HERE, f"libb200moe_i{inter}.so")
 
-SOURCES = ["abi.cu", "route_sort.cu", "router_gemm.cu", "router_tc.cu", "quant.cu", "preshuffle.cu", "reduce.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "shared_tc.cu", "sidecar.cu", "tail.cu"]
+SOURCES = ["abi.cu", "route_sort.cu", "router_gemm.cu", "router_tc.cu", "quant.cu", "preshuffle.cu", "reduce.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "ep_sync.cu", "shared_tc.cu", "sidecar.cu", "tail.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]
 

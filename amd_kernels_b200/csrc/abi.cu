@@ -40,6 +40,7 @@ int set_wait_limit_routed(unsigned long long ns);
 int set_wait_limit_shared(unsigned long long ns);
 int set_wait_limit_pair(unsigned long long ns);
 int set_wait_limit_router(unsigned long long ns);
+int set_wait_limit_ep_sync(unsigned long long ns);
 
 static Workspace carve(uint8_t* base, int64_t tokens, int num_experts, bool with_router = false) {
   Workspace ws{};
@@ -95,6 +96,7 @@ extern "C" int b200moe_set_wait_limit_ns(uint64_t ns) {
   if (!r) r = b200moe::set_wait_limit_shared(ns);
   if (!r) r = b200moe::set_wait_limit_pair(ns);
   if (!r) r = b200moe::set_wait_limit_router(ns);
+  if (!r) r = b200moe::set_wait_limit_ep_sync(ns);
   return r;
 }
 

@@ -102,7 +102,10 @@ class PeerBuffers:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         self.max_pairs, self.capacity = max_pairs, max_pairs * world
         shapes = {"slots": ((max_pairs, H), torch.bfloat16), "codes": ((self.capacity, H // 2), torch.uint8),
-                  "scales": ((self.capacity, H // 32), torch.uint8), "meta": ((4, self.capacity), torch.int32)}
+                  "scales": ((self.capacity, H // 32), torch.uint8), "meta": ((4, self.capacity), torch.int32),
+                  # the ordering points of a step (b200moe_ep_sync): one flag per source rank, and the W x W matrix of
+                  # row counts every rank deposits its row of
+                  "flags": ((64,), torch.int32), "matrix": ((world, world), torch.int64)}
         self.local, self.ptrs, self._handles = {}, {}, []
         dev = torch.device("cuda", torch.cuda.current_device())
         for name, (shape, dtype) in shapes.items():
@@ -154,7 +157,8 @@ class ExpertParallelMoe:
             dev = torch.device("cuda", torch.cuda.current_device())
             self._dest = torch.empty(self.peer.max_pairs, dtype=torch.int32, device=dev)
             self._counts = torch.zeros(self.world, dtype=torch.int64, device=dev)
-            self._matrix = torch.zeros((self.world, self.world), dtype=torch.int64, device=dev)
+            self._matrix = self.peer.local["matrix"]  # every rank stores its row of counts here (and in every peer's copy)
+            self._epoch = torch.zeros(1, dtype=torch.int32, device=dev)
             self._seg_start = torch.zeros(self.world, dtype=torch.int32, device=dev)
             self._dst_base = torch.zeros(self.world, dtype=torch.int64, device=dev)
             self._recv_pairs = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -237,6 +241,19 @@ class ExpertParallelMoe:
             return back.index_select(0, where.long()).view(tokens, TOPK, H)
         return chain.reduce_rows(back, where, tokens)
 
+    def _sync(self, stream, counts: bool = False):
+        """One ordering point between the ranks (``b200moe_ep_sync``: flags over the peer mappings, no collective call);
+        ``counts``: the launch also deposits this rank's row of the send-count matrix with every rank."""
+        import ctypes
+        from . import chain
+        from ... import _lib
+        peer = self.peer
+        _lib.check(_lib.load().b200moe_ep_sync(
+            peer.ptrs["flags"], peer.ptrs["matrix"] if counts else None,
+            ctypes.c_void_p(self._counts.data_ptr()) if counts else None, self.world, self.rank,
+            ctypes.c_void_p(self._epoch.data_ptr()), ctypes.c_void_p(chain.status_word(self._epoch.device).data_ptr()),
+            stream), "ep_sync")
+
     def _forward_peer(self, x, wt, ids, return_partials):
         """The fused form: (1) the pairs are grouped by destination rank by the routing-sort kernel; (2) one kernel
         quantises every pair's row and stores it into the destination's receive buffers; (3) the grouped GEMMs run on
@@ -253,7 +270,7 @@ class ExpertParallelMoe:
         _lib.check(lib.b200moe_ep_dest(p(ids), tokens, self.world, self.experts // self.world,
                                        int(self.placement == "interleaved"), p(dest), p(self._counts), st), "ep_dest")
         send = chain.moe_sort(dest.view(tokens, TOPK), wt, 1, self.world)       # send order: pairs grouped by rank
-        dist.all_gather_into_tensor(self._matrix, self._counts, group=self.group)  # matrix[s][d]: rows from rank s to rank d
+        self._sync(st, counts=True)                                         # matrix[s][d]: rows from rank s to rank d
         _lib.check(lib.b200moe_ep_offsets(p(self._matrix), self.world, self.rank, p(self._seg_start), p(self._dst_base),
                                           p(self._recv_pairs), st), "ep_offsets")
         self._recv_rows = self._recv_pairs
@@ -262,12 +279,12 @@ class ExpertParallelMoe:
             self.world, self.rank, self.experts // self.world, int(self.placement == "interleaved"), peer.ptrs["codes"],
             peer.ptrs["scales"], peer.ptrs["meta"], p(self._dst_base), p(self._seg_start), peer.capacity,
             p(chain.status_word(dev)), st), "quant_push")
-        dist.all_reduce(self._fence, group=self.group)                        # every rank's rows have landed
+        self._sync(st)                                                        # every rank's rows have landed
         # the receive buffers are used at their full capacity: the sort takes the number of rows that arrived from the
         # device, so it never has to reach the host; meta is four column arrays: expert, weight bits, source pair, rank
         cols = peer.local["meta"]
         self.experts_on_rows(peer.local["codes"], peer.local["scales"], cols[0], cols[1].view(torch.float32),
                              peer.capacity, cols[3], cols[2], live=self._recv_pairs)
-        dist.all_reduce(self._fence, group=self.group)                        # every rank's result rows have landed
+        self._sync(st)                                                        # every rank's result rows have landed
         slots = peer.local["slots"][:tokens * TOPK].view(tokens, TOPK, H)
         return slots.clone() if return_partials else chain.reduce_slots(slots)

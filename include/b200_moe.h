@@ -180,6 +180,18 @@ int b200moe_ep_dest(const int32_t* ids, int64_t tokens, int world, int experts_p
 int b200moe_ep_offsets(const int64_t* matrix, int world, int rank, int32_t* seg_start, int64_t* dst_base,
                        int32_t* recv_pairs, void* stream);
 
+/* Expert parallel: one ordering point between the ranks of a node, over peer mappings instead of a collective call.
+ * peer_flags[r]: rank r's flag array (int32 [world], zero at start, writable by every rank); the launch stores this rank's
+ * next epoch into slot `rank` of every peer's array and waits (bounded: status B200MOE_DEV_TIMEOUT) until every slot of its
+ * own array has reached it. `epoch_counter`: a device int32 local to the rank, zero at start, advanced by the launch (so the
+ * call can be captured in a CUDA graph); the ranks must make the same sequence of calls. With `my_counts` (int64 [world],
+ * rows this rank sends to every rank) and peer_matrices[r] (rank r's int64 [world][world]): also stores the counts as row
+ * `rank` of every peer's matrix before the flag, which replaces the all-gather of the send plan. (The reference's own
+ * collectives order their ranks with flags in IPC pools the same way: amd_kernels/collectives/pull_collectives_ranks4/
+ * kernel.py:3-20.) */
+int b200moe_ep_sync(void* const* peer_flags, void* const* peer_matrices, const int64_t* my_counts, int world, int rank,
+                    int32_t* epoch_counter, int32_t* status, void* stream);
+
 /* Expert-parallel dispatch fused with the activation quantisation (no counterpart in the reference; its multi-GPU input
  * hand-off is the all-gather of prepared inputs, MOE/prepared_input.py:116-209). send_ids / send_w / send_rank describe
  * this rank's 4T pairs grouped by destination rank (b200moe_permute on the destination ranks with bm = 1: sorted_ids,

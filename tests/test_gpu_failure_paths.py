@@ -115,3 +115,39 @@ def test_the_gathering_gemm1_never_reads_outside_the_tokens(C, small):
     assert torch.equal(h[kept], good[kept])  # rows whose entry was left alone are unchanged
     assert not bool(h[~kept].any())  # a padding row's h is zero (codes of 0.0)
     assert torch.equal(C.grouped_gemm1_gather(q, s, sort, w)[0][:nv], good)
+
+
+def test_an_ordering_point_whose_peer_never_arrives_times_out(C):
+    """b200moe_ep_sync with a second rank that does not exist (its flag array is this rank's own, so nobody ever raises
+    slot 1): the launch gives up after the lowered limit with B200MOE_DEV_TIMEOUT, the context stays usable and a
+    one-rank ordering point passes at once. No second GPU, no collective library, nothing traps."""
+    import ctypes
+    from amd_kernels_b200 import _lib
+    lib = _lib.load()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    matrix = torch.zeros((2, 2), dtype=torch.int64, device="cuda")
+    counts = torch.tensor([5, 7], dtype=torch.int64, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = C.status_word(flags.device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    two = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr())
+    two_m = (ctypes.c_void_p * 2)(matrix.data_ptr(), matrix.data_ptr())
+    C.set_wait_limit_ns(20_000_000)
+    try:
+        t0 = time.perf_counter()
+        _lib.check(lib.b200moe_ep_sync(two, two_m, p(counts), 2, 0, p(epoch), p(status), stream), "ep_sync")
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+    finally:
+        C.set_wait_limit_ns(2_000_000_000)
+    assert C.last_status() == _lib.DEV_TIMEOUT
+    assert elapsed < 5.0
+    assert int(epoch.item()) == 1 and matrix[0].tolist() == [5, 7]  # the payload and the epoch were still written
+    one = (ctypes.c_void_p * 1)(flags.data_ptr())
+    status.zero_()
+    for expect in (2, 3):
+        _lib.check(lib.b200moe_ep_sync(one, None, None, 1, 0, p(epoch), p(status), stream), "ep_sync")
+        torch.cuda.synchronize()
+        assert C.last_status() == 0 and int(epoch.item()) == expect and int(flags[0].item()) == expect
+
