@@ -59,9 +59,14 @@ SIGNATURES = {
     "b200moe_gemm1_swiglu_quant_pair": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
     "b200moe_gemm1_swiglu_quant_wide": (c_int, [_P, c_int, _P, _P, _P, _P, c_int64, _P, _P, _P, _P]),
     "b200moe_gemm1_swiglu_quant_gather": (c_int, [_P, c_int, _P, _P, c_int64, c_int, _P, _P, _P, c_int64, _P, _P, _P, _P]),
+    "b200moe_gemm1_swiglu_quant_gather_range": (c_int, [_P, c_int, _P, _P, c_int64, c_int, _P, _P, _P, c_int64, _P, _P, _P,
+                                                        c_int, _P, _P]),
+    "b200moe_block_chunks": (c_int, [_P, c_int, c_int, _P, _P]),
     "b200moe_gemm2_weighted": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_weighted_peer": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P, c_int,
                                             c_int64, _P, _P]),
+    "b200moe_gemm2_weighted_peer_range": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int64, _P, _P, _P,
+                                                  c_int, c_int64, _P, c_int, _P, _P]),
     "b200moe_gemm1_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P, _P]),
     "b200moe_gemm2_simt": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int64, _P, _P]),
     "b200moe_reduce_slots": (c_int, [_P, _P, c_int64, _P, _P]),

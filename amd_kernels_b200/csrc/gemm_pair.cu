@@ -465,7 +465,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
                       const __grid_constant__ CUtensorMap map_wc, const __grid_constant__ CUtensorMap map_ws,
                       const GatherRows rows, const int32_t* __restrict__ block_expert,
                       const int32_t* __restrict__ num_valid, uint8_t* __restrict__ hq, uint8_t* __restrict__ sfh,
-                      int32_t* status, int num_experts, int max_blocks) {
+                      int32_t* status, int num_experts, int max_blocks, const int32_t* __restrict__ block_range) {
   using C = WideCfg;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::kStages];     // the stage's codes have landed
@@ -519,6 +519,14 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
     n_blocks = 0;
   }
+  // `block_range` (may be null): the launch covers the row blocks [range[0], range[1]) only (a caller that splits the row
+  // blocks into chunks, so that a following kernel can start on one chunk while this one works on the next)
+  int b_lo = 0;
+  if (block_range != nullptr) {
+    launder(block_range);
+    b_lo = max(0, min(__ldcg(block_range), n_blocks));
+    n_blocks = max(b_lo, min(__ldcg(block_range + 1), n_blocks)) - b_lo;
+  }
   const int total = n_blocks * C::kTilePairs, stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
   const int32_t* sorted_ids = rows.sorted_ids;
   launder(sorted_ids);
@@ -532,7 +540,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
       uint32_t it = 0;
       bool ok = true;
       for (int u = first; u < total && ok; u += stride) {
-        const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+        const int b = b_lo + u / C::kTilePairs, tp = u % C::kTilePairs;
         int e = __ldcg(block_expert + b);
         if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
           atomicExch(status, B200MOE_DEV_BAD_INDEX);
@@ -559,7 +567,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
     uint32_t it = 0;
     bool ok = true;
     for (int u = first; u < total && ok; u += stride) {
-      const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+      const int b = b_lo + u / C::kTilePairs, tp = u % C::kTilePairs;
       int e = __ldcg(block_expert + b);
       if (e < 0 || e >= num_experts) e = 0;  // reported by the code producer
       const int rec_lo = ((e * kW13Tiles + 2 * tp) * kK1Tiles) * 136, rec_hi = rec_lo + kK1Tiles * 136;
@@ -607,10 +615,10 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
     const uint8_t* codes = rows.codes + c * 16;
     uint32_t it = 0;
     bool ok = true;
-    int ahead = first < total ? __ldcg(sorted_ids + (first / C::kTilePairs) * 128 + 32 * gw + lane) : -1;
+    int ahead = first < total ? __ldcg(sorted_ids + (b_lo + first / C::kTilePairs) * 128 + 32 * gw + lane) : -1;
     for (int u = first; u < total && ok; u += stride) {
       const uint32_t mine = gather_row(ahead, rows);  // the input row of block row 32 gw + lane, ~0: padding
-      if (u + stride < total) ahead = __ldcg(sorted_ids + ((u + stride) / C::kTilePairs) * 128 + 32 * gw + lane);
+      if (u + stride < total) ahead = __ldcg(sorted_ids + (b_lo + (u + stride) / C::kTilePairs) * 128 + 32 * gw + lane);
       uint32_t off[8];  // byte offset of the row's codes (the host keeps tokens * H/2 below 2^32), ~0: padding
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -703,7 +711,7 @@ __global__ void __launch_bounds__(WideCfg::kThreads, 1)
     const int tr = q * 32 + lane;
     uint32_t ui = 0;
     for (int u = first; u < total; u += stride, ++ui) {
-      const int b = u / C::kTilePairs, tp = u % C::kTilePairs;
+      const int b = b_lo + u / C::kTilePairs, tp = u % C::kTilePairs;
       const int64_t row = static_cast<int64_t>(b) * 128 + tr;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull), ui & 1u, abort_v, status))) break;
       tc_fence_after();
@@ -810,14 +818,16 @@ extern "C" int b200moe_gemm1_swiglu_quant_wide(const uint8_t* w13t, int num_expe
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
   const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
   B200MOE_LAUNCH(gemm1_wide_kernel<false>, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mx, msf, mwc,
-                 mws, GatherRows{}, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
+                 mws, GatherRows{}, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128),
+                 static_cast<const int32_t*>(nullptr));
   return 0;
 }
 
-extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes,
+extern "C" int b200moe_gemm1_swiglu_quant_gather_range(const uint8_t* w13t, int num_experts, const uint8_t* codes,
                                                  const uint8_t* scales, int64_t tokens, int by_pair, const int32_t* sorted_ids,
                                                  const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows,
-                                                 uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
+                                                 uint8_t* hq, uint8_t* sfh, const int32_t* block_range, int max_ctas,
+                                                 int32_t* status, void* stream) {
   using namespace b200moe;
   using C = WideCfg;
   if (!w13t || !codes || !scales || !sorted_ids || !block_expert || !num_valid || !hq || !sfh || !status)
@@ -839,11 +849,20 @@ extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_ex
   });
   if (rc) return rc;
   const int64_t max_units = max_rows / 128 * C::kTilePairs;
-  const int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  int grid = static_cast<int>(max_units < sm_count() ? max_units : sm_count());
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   const GatherRows rows{codes, scales, sorted_ids, tokens, by_pair ? 1 : 0};
   B200MOE_LAUNCH(gemm1_wide_kernel<true>, grid, C::kThreads, C::kSmemBytes, static_cast<cudaStream_t>(stream), mwc, mwc, mwc,
-                 mws, rows, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128));
+                 mws, rows, block_expert, num_valid, hq, sfh, status, num_experts, static_cast<int>(max_rows / 128), block_range);
   return 0;
+}
+
+extern "C" int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, const uint8_t* codes,
+                                                 const uint8_t* scales, int64_t tokens, int by_pair, const int32_t* sorted_ids,
+                                                 const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows,
+                                                 uint8_t* hq, uint8_t* sfh, int32_t* status, void* stream) {
+  return b200moe_gemm1_swiglu_quant_gather_range(w13t, num_experts, codes, scales, tokens, by_pair, sorted_ids, block_expert,
+                                                 num_valid, max_rows, hq, sfh, nullptr, 0, status, stream);
 }
 
 extern "C" int b200moe_gemm1_pair_supported(void) { return b200moe::resident_pairs() > 0 ? 1 : 0; }

@@ -88,6 +88,10 @@ struct EpilogueArgs {
   int world;
   int64_t peer_rows;  // rows of every rank's slot buffer
   int32_t* status;
+  // may be null; otherwise the launch covers the row blocks [block_range[0], block_range[1]) only (a caller that splits the
+  // row blocks into chunks, so that this kernel can start on one chunk while its predecessor works on the next)
+  const int32_t* block_range;
+  int max_ctas;  // host side only: > 0 caps the grid (leaves SMs to a kernel that runs beside this one)
 };
 
 // What the GEMM2 epilogue needs to place a result row, held in registers / shared memory (never indexed dynamically
@@ -206,6 +210,13 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     if (threadIdx.x == 0) atomicExch(status, B200MOE_DEV_BAD_INDEX);
     n_blocks = 0;
   }
+  int b_lo = 0;
+  if (ep.block_range != nullptr) {
+    const int32_t* range = ep.block_range;
+    launder(range);
+    b_lo = max(0, min(__ldcg(range), n_blocks));
+    n_blocks = max(b_lo, min(__ldcg(range + 1), n_blocks)) - b_lo;
+  }
   const int total_units = n_blocks * C::kTilesM;
 
   if (warp == 0) {
@@ -217,12 +228,12 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
       uint32_t it = 0, slot = 0, ph = 1u, base = tiles, full = full0, empty = empty0;
       // the expert id of a unit is fetched one unit ahead: a GEMM2 unit is only three stages long, and an L2 round trip
       // in front of each would leave the copy queue short
-      int e_ahead = static_cast<int>(blockIdx.x) < total_units ? __ldcg(block_expert + blockIdx.x / C::kTilesM) : 0;
+      int e_ahead = static_cast<int>(blockIdx.x) < total_units ? __ldcg(block_expert + b_lo + blockIdx.x / C::kTilesM) : 0;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int b = u / C::kTilesM, mt = u % C::kTilesM;
+        const int b = b_lo + u / C::kTilesM, mt = u % C::kTilesM;
         int e = e_ahead;
         const int un = u + static_cast<int>(gridDim.x);
-        if (un < total_units) e_ahead = __ldcg(block_expert + un / C::kTilesM);
+        if (un < total_units) e_ahead = __ldcg(block_expert + b_lo + un / C::kTilesM);
         if (e < 0 || e >= num_experts) {  // never form an address from an expert id outside the weights
           atomicExch(status, B200MOE_DEV_BAD_INDEX);
           e = 0;
@@ -350,7 +361,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
     float ahead_wt = 0.0f;
     for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++ui) {
       if (C::kEpiGroups == 2 && static_cast<int>(ui & 1u) != group) continue;  // group g owns accumulator buffer g
-      const int b = u / C::kTilesM, mt = u % C::kTilesM;
+      const int b = b_lo + u / C::kTilesM, mt = u % C::kTilesM;
       const uint32_t acc = ui & 1u, aph = (ui >> 1) & 1u;
       const int64_t row0 = static_cast<int64_t>(b) * BM;
       __nv_bfloat16* my_dst = nullptr;
@@ -374,7 +385,7 @@ __global__ void __launch_bounds__((Cfg<MODE, BM>::kThreads), 1)
         const int un = u + static_cast<int>(gridDim.x);
         have_ahead = un < total_units;
         if (have_ahead && et < BM) {
-          const int64_t r1 = static_cast<int64_t>(un / C::kTilesM) * BM + et;
+          const int64_t r1 = static_cast<int64_t>(b_lo + un / C::kTilesM) * BM + et;
           ahead_sid = __ldcg(sorted_ids + r1);
           ahead_wt = __ldcg(sorted_w + r1);
         }
@@ -956,7 +967,8 @@ static int launch(const CUtensorMap& mx, const uint8_t* w_tiles, const uint8_t* 
   if (rc) return rc;
   const int64_t max_units = max_rows / BM * C::kTilesM;
   const int64_t ctas = sm_count();
-  const int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
+  int grid = static_cast<int>(max_units < ctas ? max_units : ctas);
+  if (ep.max_ctas > 0 && grid > ep.max_ctas) grid = ep.max_ctas;
   if (grid <= 0) return 0;
   B200MOE_LAUNCH((grouped_gemm_kernel<MODE, BM>), grid, C::kThreads, C::kSmemBytes, stream, mx, w_tiles, sf_x, block_expert, num_valid, ep, status, num_experts, static_cast<int>(max_rows / BM));
   return 0;
@@ -1096,12 +1108,12 @@ extern "C" int b200moe_gemm2_weighted(const uint8_t* w2t, int num_experts, const
                       status, stream);
 }
 
-extern "C" int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+extern "C" int b200moe_gemm2_weighted_peer_range(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
                                            const int32_t* block_expert, const int32_t* num_valid,
                                            const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm,
                                            int64_t tokens, const int32_t* row_rank, const int32_t* row_pair,
-                                           void* const* peer_slots, int world, int64_t peer_rows, int32_t* status,
-                                           void* stream) {
+                                           void* const* peer_slots, int world, int64_t peer_rows,
+                                           const int32_t* block_range, int max_ctas, int32_t* status, void* stream) {
   if (!row_rank || !row_pair || !peer_slots || world < 1 || world > 8 || peer_rows < 1 || !status) return B200MOE_E_ARG;
   b200moe::EpilogueArgs ep{};
   for (int r = 0; r < 8; ++r) {
@@ -1113,6 +1125,19 @@ extern "C" int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, 
   ep.world = world;
   ep.peer_rows = peer_rows;
   ep.status = status;
+  ep.block_range = block_range;
+  ep.max_ctas = max_ctas;
   return gemm2_common(w2t, num_experts, hq, sfh, block_expert, num_valid, sorted_ids, sorted_w, max_rows, bm, tokens, ep,
                       status, stream);
+}
+
+extern "C" int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                           const int32_t* block_expert, const int32_t* num_valid,
+                                           const int32_t* sorted_ids, const float* sorted_w, int64_t max_rows, int bm,
+                                           int64_t tokens, const int32_t* row_rank, const int32_t* row_pair,
+                                           void* const* peer_slots, int world, int64_t peer_rows, int32_t* status,
+                                           void* stream) {
+  return b200moe_gemm2_weighted_peer_range(w2t, num_experts, hq, sfh, block_expert, num_valid, sorted_ids, sorted_w, max_rows,
+                                           bm, tokens, row_rank, row_pair, peer_slots, world, peer_rows, nullptr, 0, status,
+                                           stream);
 }

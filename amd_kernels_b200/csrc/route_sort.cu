@@ -392,6 +392,18 @@ __global__ void ep_offsets_kernel(const int64_t* __restrict__ matrix, int world,
   }
 }
 
+// The sorted row blocks split into `chunks` runs of (nearly) equal length: ranges[i] = {first block, one past the last} of
+// run i. The count of blocks is on the device only (num_valid), hence a kernel.
+__global__ void block_chunks_kernel(const int32_t* __restrict__ num_valid, int bm, int chunks, int32_t* __restrict__ ranges) {
+  pdl_enter(num_valid);
+  const int i = threadIdx.x;
+  if (i < chunks) {
+    const int64_t n = max(0, __ldcg(num_valid)) / bm;
+    ranges[2 * i] = static_cast<int32_t>(n * i / chunks);
+    ranges[2 * i + 1] = static_cast<int32_t>(n * (i + 1) / chunks);
+  }
+}
+
 // bm = 1 (no padding) serves the expert-parallel send order: pairs grouped by destination rank
 static int shift_of(int bm) { return bm == 1 ? 0 : bm == 16 ? 4 : bm == 32 ? 5 : bm == 64 ? 6 : bm == 128 ? 7 : -1; }
 
@@ -516,6 +528,13 @@ extern "C" int b200moe_ep_offsets(const int64_t* matrix, int world, int rank, in
     return B200MOE_E_ARG;
   B200MOE_LAUNCH(ep_offsets_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), matrix, world, rank, seg_start, dst_base,
                  recv_pairs);
+  return 0;
+}
+
+extern "C" int b200moe_block_chunks(const int32_t* num_valid, int bm, int chunks, int32_t* ranges, void* stream) {
+  using namespace b200moe;
+  if (!num_valid || !ranges || chunks < 1 || chunks > 32 || (bm != 16 && bm != 32 && bm != 64 && bm != 128)) return B200MOE_E_ARG;
+  B200MOE_LAUNCH(block_chunks_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), num_valid, bm, chunks, ranges);
   return 0;
 }
 

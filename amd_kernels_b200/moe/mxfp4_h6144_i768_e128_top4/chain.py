@@ -322,23 +322,36 @@ def grouped_gemm1_wide(xq_sorted, sfx, sort: SortBuffers, w: MoeWeights):
     return hq, sfh
 
 
-def grouped_gemm1_gather(codes, scales, sort: SortBuffers, w: MoeWeights, by_pair: bool = False):
+def block_chunks(sort: SortBuffers, chunks: int) -> torch.Tensor:
+    """int32 [chunks, 2] on the device: the sorted row blocks in ``chunks`` runs of nearly equal length (first block, one past
+    the last), for ``grouped_gemm1_gather`` / ``grouped_gemm2_peer`` with ``block_range``. Nothing reaches the host."""
+    ranges = torch.empty((chunks, 2), dtype=torch.int32, device=sort.num_valid.device)
+    _lib.check(_lib.load().b200moe_block_chunks(_ptr(sort.num_valid), sort.bm, chunks, _ptr(ranges),
+                                                _stream(ranges.device)), "block_chunks")
+    return ranges
+
+
+def grouped_gemm1_gather(codes, scales, sort: SortBuffers, w: MoeWeights, by_pair: bool = False, block_range=None,
+                         max_ctas: int = 0, out=None):
     """``grouped_gemm1`` at block height 128 straight from the UNSORTED row-major quantised tokens (``quant_mxfp4``'s codes
     [T, 3072] and scales [T, 192]): the kernel gathers each block's rows by ``sort.sorted_ids`` itself, the way the
     reference's prefill GEMM1 reads through sorted_token_ids (gemm1_prefill_h6144_i768.py:560-598). The same h codes and
     scale atoms as ``quant_dispatch`` + ``grouped_gemm1``. ``by_pair``: the input holds one row per (token, slot) pair
-    instead of one per token (rows that arrived from other ranks)."""
+    instead of one per token (rows that arrived from other ranks). ``block_range`` (a row of ``block_chunks``): only those
+    row blocks; ``max_ctas``: at most that many CTAs; ``out``: the (hq, sfh) buffers of an earlier call on the same sort."""
     if sort.bm != 128:
         raise ValueError("the gathering GEMM1 serves block height 128")
     dev = codes.device
     tokens = sort.tokens
-    hq = torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev)
-    sfh = torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev)
-    _lib.check(w.lib().b200moe_gemm1_swiglu_quant_gather(_ptr(w.w13), w.num_experts, _ptr(codes), _ptr(scales), tokens,
-                                                         int(by_pair), _ptr(sort.sorted_ids), _ptr(sort.block_expert),
-                                                         _ptr(sort.num_valid), sort.max_rows, _ptr(hq), _ptr(sfh),
-                                                         _ptr(status_word(dev)), _stream(dev)),
-               "gemm1_swiglu_quant_gather")
+    if out is None:
+        out = (torch.empty((sort.max_rows, w.intermediate // 2), dtype=torch.uint8, device=dev),
+               torch.empty((sort.max_rows // sort.bm, w.intermediate // 128, 512), dtype=torch.uint8, device=dev))
+    hq, sfh = out
+    _lib.check(w.lib().b200moe_gemm1_swiglu_quant_gather_range(
+        _ptr(w.w13), w.num_experts, _ptr(codes), _ptr(scales), tokens, int(by_pair), _ptr(sort.sorted_ids),
+        _ptr(sort.block_expert), _ptr(sort.num_valid), sort.max_rows, _ptr(hq), _ptr(sfh),
+        None if block_range is None else _ptr(block_range), int(max_ctas), _ptr(status_word(dev)), _stream(dev)),
+        "gemm1_swiglu_quant_gather")
     return hq, sfh
 
 
@@ -374,16 +387,16 @@ def grouped_gemm2(hq, sfh, sort: SortBuffers, w: MoeWeights, slots=None):
 
 
 def grouped_gemm2_peer(hq, sfh, sort: SortBuffers, w: MoeWeights, row_rank, row_pair, peer_ptrs, world: int,
-                       peer_rows: int):
+                       peer_rows: int, block_range=None, max_ctas: int = 0):
     """GEMM2 whose result rows go straight into the slot buffers of the ranks that own the pairs (expert parallel):
-    ``row_rank`` / ``row_pair`` int32 [4 * sort.tokens], ``peer_ptrs`` a ctypes array of ``world`` device pointers."""
+    ``row_rank`` / ``row_pair`` int32 [4 * sort.tokens], ``peer_ptrs`` a ctypes array of ``world`` device pointers.
+    ``block_range`` / ``max_ctas`` as in ``grouped_gemm1_gather``."""
     dev = hq.device
-    _lib.check(w.lib().b200moe_gemm2_weighted_peer(_ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh),
-                                                       _ptr(sort.block_expert), _ptr(sort.num_valid),
-                                                       _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), sort.max_rows,
-                                                       sort.bm, sort.tokens, _ptr(row_rank), _ptr(row_pair), peer_ptrs,
-                                                       world, peer_rows, _ptr(status_word(dev)), _stream(dev)),
-               "gemm2_weighted_peer")
+    _lib.check(w.lib().b200moe_gemm2_weighted_peer_range(
+        _ptr(w.w2), w.num_experts, _ptr(hq), _ptr(sfh), _ptr(sort.block_expert), _ptr(sort.num_valid),
+        _ptr(sort.sorted_ids), _ptr(sort.sorted_weights), sort.max_rows, sort.bm, sort.tokens, _ptr(row_rank),
+        _ptr(row_pair), peer_ptrs, world, peer_rows, None if block_range is None else _ptr(block_range), int(max_ctas),
+        _ptr(status_word(dev)), _stream(dev)), "gemm2_weighted_peer")
 
 
 def simt_gemm1(x_quant, sort: SortBuffers, w: MoeWeights, rows=None):

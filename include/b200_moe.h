@@ -235,6 +235,17 @@ int b200moe_gemm1_swiglu_quant_gather(const uint8_t* w13t, int num_experts, cons
                                       int64_t tokens, int by_pair, const int32_t* sorted_ids, const int32_t* block_expert,
                                       const int32_t* num_valid, int64_t max_rows, uint8_t* hq, uint8_t* sfh,
                                       int32_t* status, void* stream);
+/* The same launch restricted to the row blocks [block_range[0], block_range[1]) (device int32 pair, may be null: all) and
+ * to at most `max_ctas` CTAs (0: one per SM). A caller splits the row blocks into chunks (b200moe_block_chunks) so that the
+ * kernel that consumes hq can start on one chunk while this one works on the next, beside it on the remaining SMs. */
+int b200moe_gemm1_swiglu_quant_gather_range(const uint8_t* w13t, int num_experts, const uint8_t* codes, const uint8_t* scales,
+                                            int64_t tokens, int by_pair, const int32_t* sorted_ids,
+                                            const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows,
+                                            uint8_t* hq, uint8_t* sfh, const int32_t* block_range, int max_ctas,
+                                            int32_t* status, void* stream);
+/* ranges int32 [chunks][2]: the sorted row blocks (num_valid / bm of them, a device count) in `chunks` runs of nearly equal
+ * length; chunks <= 32. */
+int b200moe_block_chunks(const int32_t* num_valid, int bm, int chunks, int32_t* ranges, void* stream);
 int b200moe_gemm1_pair_supported(void);
 int b200moe_gemm1_swiglu_quant_pair(const uint8_t* w13t, int num_experts, const uint8_t* xq_sorted, const uint8_t* sfx,
                                     const int32_t* block_expert, const int32_t* num_valid, int64_t max_rows, uint8_t* hq,
@@ -272,6 +283,14 @@ int b200moe_gemm2_weighted_peer(const uint8_t* w2t, int num_experts, const uint8
                                 const float* sorted_w, int64_t max_rows, int bm, int64_t tokens, const int32_t* row_rank,
                                 const int32_t* row_pair, void* const* peer_slots, int world, int64_t peer_rows, int32_t* status,
                                 void* stream);
+/* b200moe_gemm2_weighted_peer on the row blocks [block_range[0], block_range[1]) only (may be null: all), on at most
+ * `max_ctas` CTAs (0: one per SM). */
+int b200moe_gemm2_weighted_peer_range(const uint8_t* w2t, int num_experts, const uint8_t* hq, const uint8_t* sfh,
+                                      const int32_t* block_expert, const int32_t* num_valid, const int32_t* sorted_ids,
+                                      const float* sorted_w, int64_t max_rows, int bm, int64_t tokens,
+                                      const int32_t* row_rank, const int32_t* row_pair, void* const* peer_slots, int world,
+                                      int64_t peer_rows, const int32_t* block_range, int max_ctas, int32_t* status,
+                                      void* stream);
 
 /* Plain CUDA-core versions of the two grouped GEMMs on checkpoint-layout weights and row-major activations, same
  * outputs and output layouts as the tcgen05 kernels. They exist so the tensor-core kernels and the preshuffle can be

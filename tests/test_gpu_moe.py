@@ -127,6 +127,41 @@ def test_cta_pair_gemm1_equals_single_cta_gemm1(C, layer, tokens, kind):
                           atoms_to_rowmajor(f_s.cpu().numpy(), 128)[:nv][live.cpu().numpy()])
 
 
+@pytest.mark.parametrize("tokens,chunks", [(2048, 4), (3000, 3), (700, 5)])
+def test_grouped_gemms_by_block_ranges_equal_one_launch(C, layer, tokens, chunks):
+    """The gathering GEMM1 and the peer-storing GEMM2 restricted to runs of row blocks (device-side ranges from
+    ``block_chunks``), on capped grids, one run after the other: the same bits as one launch over all blocks."""
+    import ctypes
+    raw, w, _, _ = layer
+    gen = torch.Generator().manual_seed(91 + tokens)
+    xb, _ = orc.make_inputs(gen, tokens)
+    ids, wts = make_routing(tokens, "uniform" if tokens != 700 else "hot", seed=tokens)
+    sb = C.moe_sort(dev(ids), dev(wts), 128, w.num_experts)
+    q, s = C.mxfp4_quant(bf16_dev(xb))
+    nv = int(sb.num_valid[0])
+    ranges = C.block_chunks(sb, chunks)
+    r = ranges.cpu().numpy()
+    assert r[0, 0] == 0 and r[-1, 1] == nv // 128 and (r[1:, 0] == r[:-1, 1]).all() and (r[:, 1] >= r[:, 0]).all()
+    full_h, full_s = C.grouped_gemm1_gather(q, s, sb, w)
+    out = None
+    for c in range(chunks):
+        out = C.grouped_gemm1_gather(q, s, sb, w, block_range=ranges[c], max_ctas=0 if c == 0 else 84, out=out)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert torch.equal(out[0][:nv], full_h[:nv]) and torch.equal(out[1][:nv // 128], full_s[:nv // 128])
+    want = C.grouped_gemm2(full_h, full_s, sb, w)
+    got = torch.zeros_like(want)
+    pairs = tokens * 4
+    rank0 = torch.zeros(pairs, dtype=torch.int32, device="cuda")
+    ident = torch.arange(pairs, dtype=torch.int32, device="cuda")
+    one = (ctypes.c_void_p * 1)(got.data_ptr())
+    for c in range(chunks):
+        C.grouped_gemm2_peer(full_h, full_s, sb, w, rank0, ident, one, 1, pairs, block_range=ranges[c], max_ctas=64)
+    torch.cuda.synchronize()
+    assert C.last_status() == 0
+    assert torch.equal(got, want)
+
+
 def test_config0_against_reference_golden(C, layer):
     """Configuration 0 (T=16) end to end against the output of the reference's own w4a4_moe_ref."""
     raw, w, xb, lg = layer
