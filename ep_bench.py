@@ -218,7 +218,7 @@ def measure(args, rank, world, local, tokens_global, zipf):
                     "combine": "GEMM2 epilogue stores into the owner's slot buffer over NVLink peer mappings" if layer.peer
                     else "NCCL all-to-all of bf16 slot rows",
                     "max_rows_received_by_a_rank": max_rows, "mean_rows_received_per_rank": mean_rows,
-                    "timing": ("CUDA-graph replay of the whole step (collectives included)" if graphs else "eager calls")
+                    "timing": ("CUDA-graph replay of the whole step (ordering points between the ranks included)" if graphs else "eager calls")
                     + ", CUDA events per step on every rank after the untimed L2 flush, max over ranks"})
         line = {"metric": "moe_layer_tokens_per_s", "value": tokens_global / (per_step * 1e-3), "unit": "tokens/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
