@@ -350,9 +350,11 @@ def gemm1_kernel_name(k):
 
 
 def gemm1_hbm_roofline(tokens, k, peaks):
-    """GEMM1 against the HBM roofline: its algorithmic bytes (the active experts' W13 codes and scales once, the sorted
+    """GEMM1 against the HBM roofline: its algorithmic bytes (the active experts' W13 codes and scales once, the input
     rows' codes and scales in, the h codes and scales out) over its launch time, over the measured copy bandwidth."""
-    byts = k["experts"] * W13_BYTES + k["rows"] * (H // 2 + H // 32) + k["rows"] * (I // 2 + I // 32)
+    # at 128-row blocks GEMM1 gathers its rows from the unsorted quantised tokens: one row per token is algorithmic input
+    rows_in = tokens if k["bm"] == 128 else k["rows"]
+    byts = k["experts"] * W13_BYTES + rows_in * (H // 2 + H // 32) + k["rows"] * (I // 2 + I // 32)
     gbs = byts / (k["g1_ms"] * 1e-3) / 1e9
     g2_bytes = k["experts"] * (EXPERT_BYTES - W13_BYTES) + k["rows"] * 408 + tokens * 4 * H * 2
     return {"kernel": gemm1_kernel_name(k), "tokens": tokens,
