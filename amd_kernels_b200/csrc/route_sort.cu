@@ -441,9 +441,12 @@ extern "C" int64_t b200moe_max_sorted_rows(int64_t tokens, int bm, int num_exper
 }
 
 extern "C" int b200moe_block_rows(int64_t tokens) {
+  // by measurement (layer time, graph replays): 16-row blocks to 480 tokens, 32-row blocks to 512, from there the 128-row
+  // path (row quantiser + GEMM1 that gathers its rows + 256 weight rows per MMA), which at 1024 / 1400 / 1728 tokens takes
+  // 196 / 208 / 211 us against 232 / 248 / 265 us with 32- and 64-row blocks (600 tokens: 190 against 194; 400: 187 against
+  // 182). The 64-row kernels stay in the library for callers that sort with that block height themselves.
   if (tokens <= 480) return 16;
-  if (tokens <= 1024) return 32;
-  if (tokens <= 1728) return 64;
+  if (tokens <= 512) return 32;
   return 128;
 }
 

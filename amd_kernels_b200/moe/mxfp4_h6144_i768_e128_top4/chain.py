@@ -603,7 +603,7 @@ def set_wait_limit_ns(ns: int) -> None:
             _lib.check(_lib.load(inter).b200moe_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")
 
 
-WARM_UP_TOKENS = (1, 64, 481, 1025, 1729, 5000)  # one-launch GEMMs, one size per block height, the 256-column GEMM1
+WARM_UP_TOKENS = (1, 64, 481, 513, 5000)  # one-launch GEMMs, one size per block height the entry uses
 
 
 def warm_up_mxfp4_moe(w, *, partials=False, workers=None):

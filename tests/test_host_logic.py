@@ -41,7 +41,7 @@ def test_sizes_match_oracle_and_reference_bounds():
         for bm in (16, 32, 64, 128):
             assert lib.b200moe_max_sorted_rows(tokens, bm, 128) == orc.max_sorted_rows(tokens, bm)
         assert lib.b200moe_workspace_bytes(tokens, 128) > tokens * 3264
-    assert [lib.b200moe_block_rows(t) for t in (1, 480, 481, 1024, 1025, 1728, 1729, 87381)] == [16, 16, 32, 32, 64, 64, 128, 128]
+    assert [lib.b200moe_block_rows(t) for t in (1, 480, 481, 512, 513, 1024, 1729, 87381)] == [16, 16, 32, 32, 128, 128, 128, 128]
     assert lib.b200moe_workspace_bytes(0, 128) == 0 and lib.b200moe_workspace_bytes(87382, 128) == 0
     # the shared expert's dense blocks: the widest block the token count fills
     assert [lib.b200moe_shared_block_rows(t) for t in (1, 16, 17, 32, 33, 64, 65, 87381)] == [16, 16, 32, 32, 64, 64, 128, 128]
